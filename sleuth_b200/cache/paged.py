@@ -6,6 +6,10 @@ Each layer application has one cache *entry*. A part asks for what its entry nee
   ``window`` positions). Entries with equal requests form a *group*; a group owns one tensor
   ``[entries, 2, pages, kv_heads, 64, head_dim]`` (index 1: 0 = keys, 1 = values), so a page number
   means the same place in every entry of the group and one block table serves them all.
+* ``LatentRequest(width, window)``: one row of ``width`` values per position, which all heads of the layer read
+  both as key and as value (attention through a low-rank latent keeps the normed latent and the shared rotated
+  key part there instead of per-head keys and values). Entries with equal requests form a group with one tensor
+  ``[entries, pages, 64, width]``; pages, block tables and windows work as for keys and values.
 * ``StateRequest(shape, dtype)``: a fixed-size state per sequence, ``[max_sequences, *shape]``, zeroed
   when a slot is taken. It is sized by the number of sequences that may be live at once, not by the
   number of pages: a state of a megabyte per sequence beside a cache of thousands of pages stays small. The Qwen3 decoder has none; a recurrent or convolutional mixer would keep
@@ -35,6 +39,12 @@ class KVRequest:
 
 
 @dataclass(frozen=True)
+class LatentRequest:
+    width: int
+    window: int = 0
+
+
+@dataclass(frozen=True)
 class StateRequest:
     shape: tuple
     dtype: torch.dtype = torch.float32
@@ -48,6 +58,15 @@ class KVView:
     group: int                  # which block table of the step's batch applies
     window: int
     writes: bool                # this application owns the entry and stores its keys and values
+
+
+@dataclass
+class LatentView:
+    """What a latent-attention part gets for its entry in one step."""
+    pool: torch.Tensor          # [pages, 64, width]
+    group: int
+    window: int
+    writes: bool
 
 
 @dataclass
@@ -78,12 +97,12 @@ class PagedCache:
             raise ValueError(f"max_sequences must be at least 1, got {max_sequences}")
         self.max_slots = int(max_sequences)
 
-        keys: list[KVRequest] = []
+        keys: list = []             # the distinct KVRequest / LatentRequest values: one group each
         self.entry_group: list[int | None] = []
         self.entry_index: list[int | None] = []
         members: list[list[int]] = []
         for e, r in enumerate(self.requests):
-            if isinstance(r, KVRequest):
+            if isinstance(r, (KVRequest, LatentRequest)):
                 if r not in keys:
                     keys.append(r)
                     members.append([])
@@ -98,8 +117,9 @@ class PagedCache:
                 raise TypeError(f"cache entry {e}: unknown request {r!r}")
         self.group_requests = keys
         self.book = CacheBook([k.window for k in keys], self.n_pages, self.max_slots, self.stride)
-        self.pools = [torch.zeros((len(m), 2, self.n_pages, k.kv_heads, PAGE_TOKENS, k.head_dim), dtype=dtype,
-                                  device=self.device) for k, m in zip(keys, members)]
+        self.pools = [torch.zeros((len(m), 2, self.n_pages, k.kv_heads, PAGE_TOKENS, k.head_dim) if isinstance(k, KVRequest)
+                                  else (len(m), self.n_pages, PAGE_TOKENS, k.width), dtype=dtype, device=self.device)
+                      for k, m in zip(keys, members)]
         self.states = {e: torch.zeros((self.max_slots, *r.shape), dtype=r.dtype, device=self.device)
                        for e, r in enumerate(self.requests) if isinstance(r, StateRequest)}
 
@@ -112,6 +132,9 @@ class PagedCache:
         if isinstance(r, KVRequest):
             g, i = self.entry_group[entry], self.entry_index[entry]
             return KVView(self.pools[g][i, 0], self.pools[g][i, 1], g, r.window, writes)
+        if isinstance(r, LatentRequest):
+            g, i = self.entry_group[entry], self.entry_index[entry]
+            return LatentView(self.pools[g][i], g, r.window, writes)
         if isinstance(r, StateRequest):
             return StateView(self.states[entry])
         return None

@@ -54,6 +54,9 @@ def find_architecture(config_json: dict) -> Architecture:
     names = config_json.get("architectures") or []
     if isinstance(names, str):
         names = [names]
+    one = config_json.get("architecture")      # some families name theirs in a single string
+    if isinstance(one, str):
+        names = [one, *names]
     for n in names:
         if n in _BY_NAME:
             return _BY_NAME[n]

@@ -136,6 +136,34 @@ __global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __nv_
   }
 }
 
+// act[t, j] = f(gu[t, j]) * gu[t, inter + j] with f = relu; float32 arithmetic. (The SiLU form has kernels of its own above.)
+template <typename T>
+__global__ void relu_gate_kernel(const T* __restrict__ gu, T* __restrict__ act, int inter, size_t total) {
+  pdl_enter();
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t step = (size_t)gridDim.x * blockDim.x;
+  for (; i < total; i += step) {
+    const size_t t = i / inter, j = i - t * inter;
+    const float g = to_f32(gu[t * 2 * inter + j]);
+    const float u = to_f32(gu[t * 2 * inter + inter + j]);
+    act[i] = from_f32<T>(fmaxf(g, 0.0f) * u);
+  }
+}
+
+// x[t, :] += again[t, :] (if given) + row[:] (if given): what a model adds to the stream between two layer applications.
+__global__ void stream_inject_kernel(float* __restrict__ x, const float* __restrict__ again, const float* __restrict__ row,
+                                     int dim, size_t total) {
+  pdl_enter();
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t step = (size_t)gridDim.x * blockDim.x;
+  for (; i < total; i += step) {
+    float v = x[i];
+    if (again) v += again[i];
+    if (row) v += row[i % dim];
+    x[i] = v;
+  }
+}
+
 static int norm_threads(int dim) {
   int t = 32;
   while (t < 512 && t * 4 < dim) t <<= 1;
@@ -230,4 +258,33 @@ extern "C" int slb_swiglu(const void* gu, void* act, int dtype, int tokens, int 
   else
     return fail(1, "swiglu: unknown dtype %d", dtype);
   return check_launch("swiglu");
+}
+
+// kind: 0 = silu (the kernels of slb_swiglu), 1 = relu.
+extern "C" int slb_gated_act(const void* gu, void* act, int dtype, int tokens, int inter, int kind, void* stream) {
+  if (kind == 0) return slb_swiglu(gu, act, dtype, tokens, inter, stream);
+  SLB_REQUIRE(kind == 1, "gated_act: unknown activation %d", kind);
+  SLB_REQUIRE(tokens >= 0 && inter > 0, "gated_act: tokens=%d inter=%d", tokens, inter);
+  if (tokens == 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  const size_t total = (size_t)tokens * inter;
+  size_t blocks = (total + 255) / 256;
+  if (blocks > (size_t)sm_count() * 16) blocks = (size_t)sm_count() * 16;
+  if (dtype == kF32)
+    launch(relu_gate_kernel<float>, dim3((int)blocks), dim3(256), 0, s, (const float*)gu, (float*)act, inter, total);
+  else if (dtype == kBF16)
+    launch(relu_gate_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(256), 0, s, (const __nv_bfloat16*)gu, (__nv_bfloat16*)act, inter, total);
+  else
+    return fail(1, "gated_act: unknown dtype %d", dtype);
+  return check_launch("gated_act");
+}
+
+extern "C" int slb_stream_inject(float* x, const float* again, const float* row, int tokens, int dim, void* stream) {
+  SLB_REQUIRE(tokens >= 0 && dim > 0, "stream_inject: tokens=%d dim=%d", tokens, dim);
+  if (tokens == 0 || (again == nullptr && row == nullptr)) return 0;
+  const size_t total = (size_t)tokens * dim;
+  size_t blocks = (total + 255) / 256;
+  if (blocks > (size_t)sm_count() * 16) blocks = (size_t)sm_count() * 16;
+  launch(stream_inject_kernel, dim3((int)blocks), dim3(256), 0, (cudaStream_t)stream, x, again, row, dim, total);
+  return check_launch("stream_inject");
 }

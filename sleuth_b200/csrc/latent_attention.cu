@@ -1,0 +1,439 @@
+// Attention through low-rank latents over a paged latent cache.
+//
+// A token's cache row holds W = R + P values: its normed latent c (R values) and one rotated key part (P values)
+// that all heads share. With the key up-projection moved onto the query (q_lat[h] = W_uk[h]^T q_plain[h]) the score
+// of head h is (q_lat[h] . c + q_rot[h] . k_rot) * scale, and the value up-projection can wait until after the
+// weighted sum: o_lat[h] = sum_j p_j c_j, value[h] = W_uv[h] o_lat[h]. So every head reads the same rows, as keys
+// (all W values) and as values (the first R).
+//
+// Kernels here:
+//   latent_post_kernel    the down-projections' float32 output -> normed query latent, normed latent and rotated key
+//                         part into the cache (norms and rotation in float32, one rounding at the store)
+//   latent_attn_kernel    causal softmax attention of all heads of a tile of tokens over the cache rows, float32
+//                         arithmetic; the rotation of the query's rotated part happens as the queries are loaded;
+//                         a long sequence's keys may be cut into slices whose partial results latent_merge_kernel joins
+//   latent_gate_kernel    y[t, h, :] = value[h, t, :] * sigmoid(g[t, h, :])
+#include "common.cuh"
+
+namespace slb {
+
+constexpr int kLatRows = 32;      // (token, head) rows of a block
+constexpr int kLatWarps = 8;
+constexpr int kLatRowsPerWarp = kLatRows / kLatWarps;
+
+// One block per token. lat[t] = [q_rank | R | P] float32.
+template <typename TO>
+__global__ void latent_post_kernel(const float* __restrict__ lat, const float* __restrict__ q_gain,
+                                   const float* __restrict__ c_gain, const float* __restrict__ cos_t,
+                                   const float* __restrict__ sin_t, TO* __restrict__ cq, TO* __restrict__ pool,
+                                   const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
+                                   const int* __restrict__ table, int stride, int q_rank, int R, int P, int rot,
+                                   float eps) {
+  pdl_enter();
+  __shared__ float scratch[33];
+  const int t = blockIdx.x;
+  const float* row = lat + (size_t)t * (q_rank + R + P);
+  float sq = 0.f, sc = 0.f;
+  for (int i = threadIdx.x; i < q_rank; i += blockDim.x) sq = fmaf(row[i], row[i], sq);
+  for (int i = threadIdx.x; i < R; i += blockDim.x) sc = fmaf(row[q_rank + i], row[q_rank + i], sc);
+  sq = block_sum(sq, scratch);
+  sc = block_sum(sc, scratch);
+  const float inv_q = 1.0f / sqrtf(sq / (float)q_rank + eps);
+  const float inv_c = 1.0f / sqrtf(sc / (float)R + eps);
+  TO* qo = cq + (size_t)t * q_rank;
+  for (int i = threadIdx.x; i < q_rank; i += blockDim.x) qo[i] = from_f32<TO>((row[i] * inv_q) * q_gain[i]);
+  if (pool == nullptr) return;
+  const int pos = tok_pos[t];
+  const int page = table[(size_t)tok_seq[t] * stride + pos / kPageTokens];
+  TO* dst = pool + ((size_t)page * kPageTokens + pos % kPageTokens) * (R + P);
+  for (int i = threadIdx.x; i < R; i += blockDim.x) dst[i] = from_f32<TO>((row[q_rank + i] * inv_c) * c_gain[i]);
+  const float* kr = row + q_rank + R;
+  const int half = rot / 2;
+  for (int i = threadIdx.x; i < P; i += blockDim.x) {
+    float v = kr[i];
+    if (i < rot) {
+      const int f = i < half ? i : i - half;
+      const float c = cos_t[(size_t)pos * half + f], s = sin_t[(size_t)pos * half + f];
+      v = i < half ? kr[i] * c - kr[i + half] * s : kr[i] * c + kr[i - half] * s;
+    }
+    dst[R + i] = from_f32<TO>(v);
+  }
+}
+
+struct LatentAttnArgs {
+  const void* q_lat;      // [H, T, R]
+  const void* q_raw;      // [T, H, dn + P]; the rotated part starts at dn
+  const void* pool;       // [pages, 64, R + P]
+  void* out;              // [H, T, R]
+  float* parts;           // splits > 1: [splits, T * H, R + 2] (sum, then running maximum and mass)
+  const float* cos_t;
+  const float* sin_t;
+  const int* seq_start;
+  const int* past;
+  const int* counts;
+  const int* table;
+  int stride, T, H, R, P, dn, rot, window, splits, chunk, tq, hb, kstride;
+  float scale;
+};
+
+// Block (x: tile of tq tokens, y: sequence, z: head chunk * splits + slice), 8 warps, 4 (token, head) rows a warp.
+// The keys are walked in chunks of `chunk` (16, 32 or 64) rows staged in shared memory as float32 with an odd row
+// stride; a lane takes a key (two with 64), then a value column (RV of them).
+template <typename T, int RV>
+__global__ void __launch_bounds__(kLatWarps * 32) latent_attn_kernel(const LatentAttnArgs a) {
+  pdl_enter();
+  extern __shared__ float smem[];
+  const int W = a.R + a.P;
+  float* Qs = smem;                                   // [32][W]
+  float* Ks = Qs + (size_t)kLatRows * W;              // [chunk][kstride]
+  float* Ps = Ks + (size_t)a.chunk * a.kstride;       // [warps][64][4]
+  const int seq = blockIdx.y;
+  const int slice = blockIdx.z % a.splits, hc = blockIdx.z / a.splits;
+  const int count = a.counts[seq], past = a.past[seq];
+  const int t0 = blockIdx.x * a.tq;
+  if (t0 >= count) return;
+  const int nt = min(a.tq, count - t0);
+  const int h0 = hc * a.hb, nh = min(a.hb, a.H - h0);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const T* q_lat = (const T*)a.q_lat;
+  const T* q_raw = (const T*)a.q_raw;
+  const T* pool = (const T*)a.pool;
+  const int tok0 = a.seq_start[seq] + t0;             // first token row of the tile
+
+  // queries: latent part as it is, rotated part turned by the token's angle
+  const int half = a.rot / 2;
+  for (int r = warp; r < kLatRows; r += kLatWarps) {
+    const int tq = r / a.hb, hh = r % a.hb;
+    const bool live = tq < nt && hh < nh;
+    float* qs = Qs + (size_t)r * W;
+    if (!live) {
+      for (int i = lane; i < W; i += 32) qs[i] = 0.f;
+      continue;
+    }
+    const int tok = tok0 + tq, h = h0 + hh, pos = past + t0 + tq;
+    const T* ql = q_lat + ((size_t)h * a.T + tok) * a.R;
+    for (int i = lane; i < a.R; i += 32) qs[i] = to_f32(ql[i]);
+    const T* qr = q_raw + ((size_t)tok * a.H + h) * (a.dn + a.P) + a.dn;
+    for (int i = lane; i < a.P; i += 32) {
+      float v = to_f32(qr[i]);
+      if (i < a.rot) {
+        const int f = i < half ? i : i - half;
+        const float c = a.cos_t[(size_t)pos * half + f], s = a.sin_t[(size_t)pos * half + f];
+        v = i < half ? v * c - to_f32(qr[i + half]) * s : v * c + to_f32(qr[i - half]) * s;
+      }
+      qs[a.R + i] = v;
+    }
+  }
+
+  // the keys this block walks
+  const int last_pos = past + t0 + nt - 1;
+  int key_lo = a.window > 0 ? max(0, past + t0 - a.window + 1) : 0;
+  key_lo = key_lo / a.chunk * a.chunk;
+  const int n_chunks = (last_pos - key_lo) / a.chunk + 1;
+  const int per = (n_chunks + a.splits - 1) / a.splits;
+  const int c_lo = slice * per, c_hi = min(n_chunks, c_lo + per);
+
+  float acc[kLatRowsPerWarp][RV];
+  float m[kLatRowsPerWarp], l[kLatRowsPerWarp];
+  int row_pos[kLatRowsPerWarp];
+#pragma unroll
+  for (int r = 0; r < kLatRowsPerWarp; ++r) {
+    m[r] = -INFINITY;
+    l[r] = 0.f;
+    const int row = warp * kLatRowsPerWarp + r;
+    const int tq = row / a.hb, hh = row % a.hb;
+    row_pos[r] = (tq < nt && hh < nh) ? past + t0 + tq : -1;
+#pragma unroll
+    for (int i = 0; i < RV; ++i) acc[r][i] = 0.f;
+  }
+  const int* trow = a.table + (size_t)seq * a.stride;
+  const float* qw = Qs + (size_t)warp * kLatRowsPerWarp * W;
+  float* pw = Ps + (size_t)warp * 64 * kLatRowsPerWarp;
+  const int keys_per_lane = a.chunk > 32 ? 2 : 1;
+
+  for (int c = c_lo; c < c_hi; ++c) {
+    const int k0 = key_lo + c * a.chunk;
+    const int nk = min(a.chunk, last_pos - k0 + 1);
+    __syncthreads();
+    // stage the chunk: rows k0 .. k0 + nk - 1 of one page (a chunk never straddles pages: 64 is a multiple of it)
+    {
+      const int page = trow[k0 / kPageTokens];
+      const T* src = pool + ((size_t)page * kPageTokens + k0 % kPageTokens) * W;
+      const int total = nk * W;
+      for (int i = threadIdx.x; i < total; i += blockDim.x) {
+        const int j = i / W, d = i - j * W;
+        Ks[(size_t)j * a.kstride + d] = to_f32(src[i]);
+      }
+      for (int i = threadIdx.x + total; i < a.chunk * W; i += blockDim.x) {
+        const int j = i / W, d = i - j * W;
+        Ks[(size_t)j * a.kstride + d] = 0.f;
+      }
+    }
+    __syncthreads();
+
+    // scores: lane = key (and key + 32)
+    float s[kLatRowsPerWarp][2];
+#pragma unroll
+    for (int r = 0; r < kLatRowsPerWarp; ++r) s[r][0] = s[r][1] = 0.f;
+    const int ja = min(lane, a.chunk - 1);
+    const float* ka = Ks + (size_t)ja * a.kstride;
+    const float* kb = Ks + (size_t)min(lane + 32, a.chunk - 1) * a.kstride;
+    if (keys_per_lane == 2) {
+      for (int d = 0; d < W; ++d) {
+        const float x0 = ka[d], x1 = kb[d];
+#pragma unroll
+        for (int r = 0; r < kLatRowsPerWarp; ++r) {
+          const float qv = qw[(size_t)r * W + d];
+          s[r][0] = fmaf(qv, x0, s[r][0]);
+          s[r][1] = fmaf(qv, x1, s[r][1]);
+        }
+      }
+    } else {
+      for (int d = 0; d < W; ++d) {
+        const float x0 = ka[d];
+#pragma unroll
+        for (int r = 0; r < kLatRowsPerWarp; ++r) s[r][0] = fmaf(qw[(size_t)r * W + d], x0, s[r][0]);
+      }
+    }
+    // softmax bookkeeping per row, probabilities to shared memory as [key][row]
+    float alpha[kLatRowsPerWarp];
+#pragma unroll
+    for (int r = 0; r < kLatRowsPerWarp; ++r) {
+      float mx = -INFINITY;
+      float sv[2];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int j = lane + 32 * u;
+        const int kpos = k0 + j;
+        const bool seen = u < keys_per_lane && j < nk && row_pos[r] >= 0 && kpos <= row_pos[r] &&
+                          (a.window <= 0 || kpos > row_pos[r] - a.window);
+        sv[u] = seen ? s[r][u] * a.scale : -INFINITY;
+        mx = fmaxf(mx, sv[u]);
+      }
+      mx = warp_max(mx);
+      const float m_new = fmaxf(m[r], mx);
+      float psum = 0.f;
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const float p = (m_new == -INFINITY || sv[u] == -INFINITY) ? 0.f : expf(sv[u] - m_new);
+        psum += p;
+        if (u < keys_per_lane) pw[(size_t)(lane + 32 * u) * kLatRowsPerWarp + r] = p;
+      }
+      psum = warp_sum(psum);
+      alpha[r] = (m[r] == -INFINITY) ? 0.f : expf(m[r] - m_new);
+      if (m_new == -INFINITY) alpha[r] = 1.f;
+      l[r] = l[r] * alpha[r] + psum;
+      m[r] = m_new;
+    }
+    __syncwarp();
+    // weighted sum of the latents: lane = value column
+#pragma unroll
+    for (int r = 0; r < kLatRowsPerWarp; ++r)
+#pragma unroll
+      for (int i = 0; i < RV; ++i) acc[r][i] *= alpha[r];
+    for (int j = 0; j < nk; ++j) {
+      const float4 p4 = *reinterpret_cast<const float4*>(pw + (size_t)j * kLatRowsPerWarp);
+      const float pr[4] = {p4.x, p4.y, p4.z, p4.w};
+      const float* kv = Ks + (size_t)j * a.kstride;
+#pragma unroll
+      for (int i = 0; i < RV; ++i) {
+        const int d = lane + 32 * i;
+        const float v = d < a.R ? kv[d] : 0.f;
+#pragma unroll
+        for (int r = 0; r < kLatRowsPerWarp; ++r) acc[r][i] = fmaf(pr[r], v, acc[r][i]);
+      }
+    }
+    __syncwarp();
+  }
+
+  // results
+#pragma unroll
+  for (int r = 0; r < kLatRowsPerWarp; ++r) {
+    if (row_pos[r] < 0) continue;
+    const int row = warp * kLatRowsPerWarp + r;
+    const int tok = tok0 + row / a.hb, h = h0 + row % a.hb;
+    if (a.splits == 1) {
+      const float inv = l[r] > 0.f ? 1.0f / l[r] : 0.f;
+      T* o = (T*)a.out + ((size_t)h * a.T + tok) * a.R;
+#pragma unroll
+      for (int i = 0; i < RV; ++i) {
+        const int d = lane + 32 * i;
+        if (d < a.R) o[d] = from_f32<T>(acc[r][i] * inv);
+      }
+    } else {
+      float* o = a.parts + ((size_t)slice * a.T * a.H + (size_t)tok * a.H + h) * (a.R + 2);
+#pragma unroll
+      for (int i = 0; i < RV; ++i) {
+        const int d = lane + 32 * i;
+        if (d < a.R) o[d] = acc[r][i];
+      }
+      if (lane == 0) {
+        o[a.R] = m[r];
+        o[a.R + 1] = l[r];
+      }
+    }
+  }
+}
+
+// One warp per (token, head): joins the slices in slice order.
+template <typename T>
+__global__ void latent_merge_kernel(const float* __restrict__ parts, T* __restrict__ out, int rows, int Tn, int H, int R,
+                                    int splits) {
+  pdl_enter();
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const int tok = row / H, h = row % H;
+  float mx = -INFINITY;
+  for (int s = 0; s < splits; ++s) mx = fmaxf(mx, parts[((size_t)s * rows + row) * (R + 2) + R]);
+  float mass = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float* p = parts + ((size_t)s * rows + row) * (R + 2);
+    if (p[R] != -INFINITY) mass += p[R + 1] * expf(p[R] - mx);
+  }
+  const float inv = mass > 0.f ? 1.0f / mass : 0.f;
+  T* o = out + ((size_t)h * Tn + tok) * R;
+  for (int d = lane; d < R; d += 32) {
+    float v = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const float* p = parts + ((size_t)s * rows + row) * (R + 2);
+      if (p[R] != -INFINITY) v = fmaf(p[d], expf(p[R] - mx), v);
+    }
+    o[d] = from_f32<T>(v * inv);
+  }
+}
+
+// y[t, h * dv + j] = val[h, t, j] * sigmoid(g[t, h * dv + j])
+template <typename T>
+__global__ void latent_gate_kernel(const T* __restrict__ val, const T* __restrict__ g, T* __restrict__ y, int Tn, int H,
+                                   int dv, size_t total) {
+  pdl_enter();
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t step = (size_t)gridDim.x * blockDim.x;
+  for (; i < total; i += step) {
+    const size_t t = i / ((size_t)H * dv);
+    const int rest = (int)(i - t * H * dv), h = rest / dv, j = rest - h * dv;
+    const float v = to_f32(val[((size_t)h * Tn + t) * dv + j]);
+    const float z = to_f32(g[i]);
+    y[i] = from_f32<T>(v * (1.0f / (1.0f + expf(-z))));
+  }
+}
+
+static int lat_rv(int R) {
+  const int need = (R + 31) / 32;
+  for (int v : {1, 2, 3, 4, 6, 8, 12, 16, 24, 32})
+    if (need <= v) return v;
+  return 0;
+}
+
+static int lat_chunk_for(int W, int& kstride, size_t& bytes) {
+  kstride = (W % 2 == 0) ? W + 1 : W;
+  for (int chunk : {64, 32, 16}) {
+    bytes = ((size_t)kLatRows * W + (size_t)chunk * kstride + (size_t)kLatWarps * 64 * kLatRowsPerWarp) * sizeof(float);
+    if (bytes <= 200 * 1024) return chunk;
+  }
+  return 0;
+}
+
+}  // namespace slb
+
+using namespace slb;
+
+extern "C" int slb_latent_post(const float* lat, const float* q_gain, const float* c_gain, const float* cos_t,
+                               const float* sin_t, void* cq, void* pool, const int* tok_seq, const int* tok_pos,
+                               const int* table, int stride, int tokens, int q_rank, int R, int P, int rot, float eps,
+                               int dtype, void* stream) {
+  SLB_REQUIRE(tokens >= 0 && q_rank > 0 && R > 0 && P >= 0 && rot >= 0 && rot <= P && rot % 2 == 0 && eps > 0.f,
+              "latent_post: tokens=%d q_rank=%d rank=%d rot_dim=%d rotated=%d", tokens, q_rank, R, P, rot);
+  SLB_REQUIRE(dtype == kF32 || dtype == kBF16, "latent_post: unknown dtype %d", dtype);
+  if (tokens == 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int widest = q_rank > R ? q_rank : R;
+  const int threads = widest > 512 ? 256 : (widest > 128 ? 128 : 64);
+  if (dtype == kF32)
+    launch(latent_post_kernel<float>, dim3(tokens), dim3(threads), 0, s, lat, q_gain, c_gain, cos_t, sin_t, (float*)cq,
+           (float*)pool, tok_seq, tok_pos, table, stride, q_rank, R, P, rot, eps);
+  else
+    launch(latent_post_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), 0, s, lat, q_gain, c_gain, cos_t, sin_t,
+           (__nv_bfloat16*)cq, (__nv_bfloat16*)pool, tok_seq, tok_pos, table, stride, q_rank, R, P, rot, eps);
+  return check_launch("latent_post");
+}
+
+// Whether the attention kernel takes these sizes (latent width and rotated width).
+extern "C" int slb_latent_attention_supported(int R, int P) {
+  int kstride;
+  size_t bytes;
+  return R > 0 && P >= 0 && lat_rv(R) > 0 && lat_chunk_for(R + P, kstride, bytes) > 0 ? 1 : 0;
+}
+
+extern "C" int slb_latent_attention(const void* q_lat, const void* q_raw, const void* pool, void* out, float* parts,
+                                    const float* cos_t, const float* sin_t, const int* seq_start, const int* past,
+                                    const int* counts, const int* table, int stride, int n_seqs, int max_count, int T,
+                                    int H, int R, int P, int dn, int rot, int window, float scale, int splits,
+                                    int dtype, void* stream) {
+  SLB_REQUIRE(n_seqs >= 0 && max_count >= 0 && T >= 0 && H > 0 && R > 0 && P >= 0 && dn >= 0 && rot >= 0 && rot <= P &&
+                  rot % 2 == 0 && splits >= 1 && window >= 0,
+              "latent_attention: seqs=%d max=%d heads=%d rank=%d rot_dim=%d splits=%d", n_seqs, max_count, H, R, P, splits);
+  SLB_REQUIRE(dtype == kF32 || dtype == kBF16, "latent_attention: unknown dtype %d", dtype);
+  SLB_REQUIRE(splits == 1 || parts != nullptr, "latent_attention: slices need scratch memory");
+  if (n_seqs == 0 || max_count == 0 || T == 0) return 0;
+  LatentAttnArgs a;
+  a.q_lat = q_lat; a.q_raw = q_raw; a.pool = pool; a.out = out; a.parts = parts; a.cos_t = cos_t; a.sin_t = sin_t;
+  a.seq_start = seq_start; a.past = past; a.counts = counts; a.table = table; a.stride = stride; a.T = T; a.H = H;
+  a.R = R; a.P = P; a.dn = dn; a.rot = rot; a.window = window; a.splits = splits; a.scale = scale;
+  size_t bytes;
+  a.chunk = lat_chunk_for(R + P, a.kstride, bytes);
+  const int rv = lat_rv(R);
+  SLB_REQUIRE(a.chunk > 0 && rv > 0, "latent_attention: a cache row of %d values (latent %d) is too wide", R + P, R);
+  a.hb = H < kLatRows ? H : kLatRows;
+  a.tq = kLatRows / a.hb;
+  const int head_chunks = (H + a.hb - 1) / a.hb;
+  const dim3 grid((max_count + a.tq - 1) / a.tq, n_seqs, head_chunks * splits), block(kLatWarps * 32);
+  cudaStream_t s = (cudaStream_t)stream;
+#define SLB_LAT(TT, V)                                                                                   \
+  do {                                                                                                   \
+    static bool raised_##V = false;                                                                      \
+    if (!raised_##V) {                                                                                   \
+      cudaFuncSetAttribute(latent_attn_kernel<TT, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); \
+      raised_##V = true;                                                                                 \
+    }                                                                                                    \
+    launch(latent_attn_kernel<TT, V>, grid, block, bytes, s, a);                                         \
+  } while (0)
+#define SLB_LAT_RV(TT)                                                                   \
+  switch (rv) {                                                                          \
+    case 1: SLB_LAT(TT, 1); break;   case 2: SLB_LAT(TT, 2); break;                      \
+    case 3: SLB_LAT(TT, 3); break;   case 4: SLB_LAT(TT, 4); break;                      \
+    case 6: SLB_LAT(TT, 6); break;   case 8: SLB_LAT(TT, 8); break;                      \
+    case 12: SLB_LAT(TT, 12); break; case 16: SLB_LAT(TT, 16); break;                    \
+    case 24: SLB_LAT(TT, 24); break; default: SLB_LAT(TT, 32); break;                    \
+  }
+  if (dtype == kF32) { SLB_LAT_RV(float) } else { SLB_LAT_RV(__nv_bfloat16) }
+#undef SLB_LAT_RV
+#undef SLB_LAT
+  int rc = check_launch("latent_attention");
+  if (rc || splits == 1) return rc;
+  const int rows = T * H;
+  if (dtype == kF32)
+    launch(latent_merge_kernel<float>, dim3((rows + 7) / 8), dim3(256), 0, s, (const float*)parts, (float*)out, rows, T, H, R, splits);
+  else
+    launch(latent_merge_kernel<__nv_bfloat16>, dim3((rows + 7) / 8), dim3(256), 0, s, (const float*)parts,
+           (__nv_bfloat16*)out, rows, T, H, R, splits);
+  return check_launch("latent_merge");
+}
+
+extern "C" int slb_latent_gate(const void* val, const void* g, void* y, int tokens, int H, int dv, int dtype,
+                               void* stream) {
+  SLB_REQUIRE(tokens >= 0 && H > 0 && dv > 0, "latent_gate: tokens=%d heads=%d width=%d", tokens, H, dv);
+  if (tokens == 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  const size_t total = (size_t)tokens * H * dv;
+  size_t blocks = (total + 255) / 256;
+  if (blocks > (size_t)sm_count() * 16) blocks = (size_t)sm_count() * 16;
+  if (dtype == kF32)
+    launch(latent_gate_kernel<float>, dim3((int)blocks), dim3(256), 0, s, (const float*)val, (const float*)g, (float*)y, tokens, H, dv, total);
+  else if (dtype == kBF16)
+    launch(latent_gate_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(256), 0, s, (const __nv_bfloat16*)val,
+           (const __nv_bfloat16*)g, (__nv_bfloat16*)y, tokens, H, dv, total);
+  else
+    return fail(1, "latent_gate: unknown dtype %d", dtype);
+  return check_launch("latent_gate");
+}

@@ -48,6 +48,9 @@ class Model:
         self.cache_requests = [self.layers[spec.schedule[self.entry_owner[c]].layer].cache_request()
                                for c in range(len(self.entry_owner))]
         self._programs: dict = {}       # per cache: the runs of the schedule prepared for the persistent kernel
+        self.pass_rows = None           # [rows, hidden] float32: vectors that schedule entries add to the stream
+        self.keeps_embedding = any(e.add_embedding for e in spec.schedule)
+        self.observe = None             # callable(schedule index, stream) after every layer application, for inspection
 
     # ---- weights ----
     def _end_names(self, which: str) -> dict[str, str]:
@@ -79,6 +82,8 @@ class Model:
         hd = self.head.declare()
         for local, name in self._end_names("head").items():
             out[name] = hd[local]
+        if self.spec.pass_rows:
+            out[self.spec.pass_rows] = ParamDecl((self.spec.pass_rows_count, self.hidden), "vector")
         return out
 
     def bind(self, tensors: dict[str, torch.Tensor]) -> None:
@@ -87,6 +92,8 @@ class Model:
             layer.bind({local: tensors[ls.names[local]] for local in layer.declare() if ls.names[local] in tensors})
         head = {local: tensors[name] for local, name in self._end_names("head").items() if name in tensors}
         self.head.bind(head, embedding_table=getattr(self.embedding, "table", None))
+        if self.spec.pass_rows:
+            self.pass_rows = tensors[self.spec.pass_rows].to(torch.float32).contiguous()
 
     # ---- one step ----
     def forward(self, b, cache, ws, logits: torch.Tensor) -> torch.Tensor:
@@ -95,6 +102,10 @@ class Model:
         mark = ws.mark()
         x = ws.take((b.T, self.hidden), torch.float32)
         self.embedding.forward(b, x)
+        x0 = None
+        if self.keeps_embedding:        # some application adds the embedding's output again: keep a copy
+            x0 = ws.take((b.T, self.hidden), torch.float32)
+            x0.copy_(x)
         schedule = self.spec.schedule
         fused = self._fused_runs(b, cache)
         i = 0
@@ -103,10 +114,16 @@ class Model:
                 i = self._run_fused(fused[i], x, b, ws)
                 continue
             e = schedule[i]
+            if e.add_embedding or e.add_row >= 0:
+                from ..kernels import ops
+                ops.stream_inject(x, x0 if e.add_embedding else None,
+                                  self.pass_rows[e.add_row] if e.add_row >= 0 else None, b.stream)
             view = cache.view(e.cache, writes=self.entry_owner[e.cache] == i)
             following = self.layers[schedule[i + 1].layer] if i + 1 < len(schedule) and (i + 1) not in fused else None
             b.next_read = lead_weight_of(following)
             self.layers[e.layer].forward(x, b, view, ws)
+            if self.observe is not None:
+                self.observe(i, x)
             i += 1
         b.next_read = None
         if logits.shape[0]:

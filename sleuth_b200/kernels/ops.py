@@ -18,6 +18,7 @@ import torch
 from . import library
 
 DT = {torch.float32: 0, torch.bfloat16: 1}
+ACTIVATIONS = {"silu": 0, "relu": 1}
 
 
 def lib() -> library.KernelLibrary:
@@ -84,6 +85,26 @@ def swiglu(gu: torch.Tensor, act: torch.Tensor, stream=None) -> None:
     _need(gu.shape == (T, 2 * inter) and gu.dtype == act.dtype and act.dtype in DT, "swiglu: shapes or dtypes")
     lib().call("slb_swiglu", _p(gu), _p(act), DT[act.dtype], T, inter,
                stream if stream is not None else current_stream())
+
+
+def gated_act(gu: torch.Tensor, act: torch.Tensor, kind: str = "silu", stream=None) -> None:
+    """act[t, j] = f(gu[t, j]) * gu[t, inter + j] with f = silu or relu."""
+    _cuda(gu, act)
+    T, inter = act.shape
+    _need(kind in ACTIVATIONS, f"gated_act: activation {kind!r} is not one of {sorted(ACTIVATIONS)}")
+    _need(gu.shape == (T, 2 * inter) and gu.dtype == act.dtype and act.dtype in DT, "gated_act: shapes or dtypes")
+    lib().call("slb_gated_act", _p(gu), _p(act), DT[act.dtype], T, inter, ACTIVATIONS[kind],
+               stream if stream is not None else current_stream())
+
+
+def stream_inject(x: torch.Tensor, again: torch.Tensor | None, row: torch.Tensor | None, stream=None) -> None:
+    """x[t] += again[t] + row: ``again`` has the stream's shape, ``row`` one value per channel; either may be None."""
+    _cuda(x, again, row)
+    T, d = x.shape
+    _need(x.dtype == torch.float32, "stream_inject: the stream is float32")
+    _need(again is None or (again.dtype == torch.float32 and again.shape == x.shape), "stream_inject: the added rows")
+    _need(row is None or (row.dtype == torch.float32 and row.numel() == d), "stream_inject: the added vector")
+    lib().call("slb_stream_inject", _p(x), _p(again), _p(row), T, d, stream if stream is not None else current_stream())
 
 
 def qkv_post(qkv, bias, q_gain, k_gain, cos, sin, q_out, k_pool, v_pool, tok_seq, tok_pos, block_table,
@@ -637,3 +658,121 @@ def sample(logits: torch.Tensor, limit: int, temperature: float, top_k: int, top
           0 < limit <= logits.shape[1], "sample: shapes")
     lib().call("slb_sample", _p(logits), logits.stride(0), logits.shape[0], limit, float(temperature), int(top_k),
                float(top_p), float(min_p), _p(uniform), _p(out), stream if stream is not None else current_stream())
+
+
+# ---- attention through low-rank latents (csrc/latent_attention.cu) ----
+def latent_post(lat, q_gain, c_gain, cos, sin, cq, pool, tok_seq, tok_pos, block_table, q_rank: int, rank: int,
+                rot_dim: int, rotated: int, eps: float, stream=None) -> None:
+    """lat [T, q_rank + rank + rot_dim] float32 (the two down-projections' output): the normed query latent goes to
+    ``cq`` [T, q_rank]; the normed latent and the rotated key part go to the token's row of ``pool``
+    [pages, 64, rank + rot_dim] (``pool`` None: nothing is stored). ``rotated``: how many leading channels of the key
+    part turn."""
+    _cuda(lat, q_gain, c_gain, cos, sin, cq, pool, tok_seq, tok_pos, block_table)
+    T = cq.shape[0]
+    _need(lat.dtype == torch.float32 and lat.shape == (T, q_rank + rank + rot_dim), "latent_post: input shape or dtype")
+    _need(cq.shape == (T, q_rank) and cq.dtype in DT, "latent_post: query latent")
+    _need(q_gain.dtype == torch.float32 and q_gain.numel() == q_rank and c_gain.dtype == torch.float32
+          and c_gain.numel() == rank, "latent_post: gains")
+    if rotated:
+        _need(cos is not None and cos.dtype == torch.float32 and cos.shape[1] == rotated // 2 and sin.shape == cos.shape,
+              "latent_post: rotation tables")
+    stride = 0
+    if pool is not None:
+        _need(pool.dtype == cq.dtype and tuple(pool.shape[1:]) == (64, rank + rot_dim), "latent_post: pool shape or dtype")
+        _need(block_table.dtype == torch.int32 and block_table.dim() == 2, "latent_post: block table")
+        stride = block_table.shape[1]
+    _need(tok_seq.dtype == torch.int32 and tok_pos.dtype == torch.int32, "latent_post: token tables are int32")
+    lib().call("slb_latent_post", _p(lat), _p(q_gain), _p(c_gain), _p(cos), _p(sin), _p(cq), _p(pool), _p(tok_seq),
+               _p(tok_pos), _p(block_table), stride, T, q_rank, rank, rot_dim, rotated, float(eps), DT[cq.dtype],
+               stream if stream is not None else current_stream())
+
+
+def latent_attention_supported(rank: int, rot_dim: int) -> bool:
+    fn = lib().dll.slb_latent_attention_supported
+    fn.argtypes, fn.restype = [ctypes.c_int, ctypes.c_int], ctypes.c_int
+    return bool(fn(int(rank), int(rot_dim)))
+
+
+def latent_splits(n_seqs: int, heads: int, max_count: int, max_len: int, sms: int | None = None) -> int:
+    """Into how many slices the keys of a step are cut: none while the step's own blocks fill the SMs, else as many
+    as it takes to give every SM about two blocks, each slice at least four pages long."""
+    sms = sms or sm_count()
+    hb = min(heads, 32)
+    blocks = n_seqs * -(-max_count // (32 // hb)) * -(-heads // hb)
+    if blocks >= sms or max_len <= 256:
+        return 1
+    return int(max(1, min(2 * sms // max(blocks, 1), max_len // 256, 64)))
+
+
+def latent_scratch_floats(tokens: int, heads: int, rank: int, splits: int) -> int:
+    return 0 if splits <= 1 else splits * tokens * heads * (rank + 2)
+
+
+def latent_attention(q_lat, q_raw, pool, out, cos, sin, seq_start, past, counts, block_table, max_count: int,
+                     heads: int, rank: int, rot_dim: int, plain_dim: int, rotated: int, window: int, scale: float,
+                     splits: int = 1, scratch=None, stream=None) -> None:
+    """Causal softmax attention of every head over the latent cache rows. q_lat [heads, T, rank]: the queries' plain
+    part carried into the latent space; q_raw [T, heads, plain_dim + rot_dim]: the up-projected queries, whose
+    rotated part (from ``plain_dim`` on) is turned as it is read; out [heads, T, rank]."""
+    _cuda(q_lat, q_raw, pool, out, cos, sin, seq_start, past, counts, block_table, scratch)
+    T = q_raw.shape[0]
+    _need(q_lat.shape == (heads, T, rank) and out.shape == (heads, T, rank), "latent_attention: latent query or output shape")
+    _need(q_raw.shape == (T, heads, plain_dim + rot_dim), "latent_attention: query shape")
+    _need(q_lat.dtype == q_raw.dtype == pool.dtype == out.dtype and out.dtype in DT, "latent_attention: dtypes")
+    _need(tuple(pool.shape[1:]) == (64, rank + rot_dim), "latent_attention: pool shape")
+    _need(block_table.dtype == torch.int32 and block_table.dim() == 2, "latent_attention: block table")
+    if rotated:
+        _need(cos is not None and cos.dtype == torch.float32 and cos.shape[1] == rotated // 2, "latent_attention: rotation tables")
+    if splits > 1:
+        _need(scratch is not None and scratch.dtype == torch.float32 and
+              scratch.numel() >= latent_scratch_floats(T, heads, rank, splits), "latent_attention: scratch for the slices")
+    n = past.numel()
+    lib().call("slb_latent_attention", _p(q_lat), _p(q_raw), _p(pool), _p(out), _p(scratch), _p(cos), _p(sin),
+               _p(seq_start), _p(past), _p(counts), _p(block_table), block_table.shape[1], n, int(max_count), T, heads,
+               rank, rot_dim, plain_dim, rotated, int(window), float(scale), int(splits), DT[out.dtype],
+               stream if stream is not None else current_stream())
+
+
+def latent_gate(val, g, y, stream=None) -> None:
+    """y[t, h, :] = val[h, t, :] * sigmoid(g[t, h, :]); val [heads, T, width], g and y [T, heads * width]."""
+    _cuda(val, g, y)
+    H, T, dv = val.shape
+    _need(g.shape == (T, H * dv) and y.shape == g.shape and val.dtype == g.dtype == y.dtype and y.dtype in DT,
+          "latent_gate: shapes or dtypes")
+    lib().call("slb_latent_gate", _p(val), _p(g), _p(y), T, H, dv, DT[y.dtype], stream if stream is not None else current_stream())
+
+
+# ---- routed experts (csrc/moe.cu) ----
+def moe_route(h, w_router, bias, choice, weight, rank, counts, place, order, top: int, stream=None) -> None:
+    """Router logits in float32, the ``top`` largest per token, softmax over those; then the (token, choice) pairs are
+    laid out expert by expert: counts [experts], place [T * top] (a pair's row in that order), order [T * top] (the
+    pair at each row). choice, rank int32 [T * top]; weight float32 [T * top]."""
+    _cuda(h, w_router, bias, choice, weight, rank, counts, place, order)
+    T, d = h.shape
+    E = w_router.shape[0]
+    _need(h.dtype in DT and w_router.dtype == torch.float32 and w_router.shape == (E, d), "moe_route: input or router matrix")
+    _need(bias is None or (bias.dtype == torch.float32 and bias.numel() == E), "moe_route: bias")
+    for t in (choice, rank, place, order):
+        _need(t.dtype == torch.int32 and t.numel() >= T * top, "moe_route: int32 tables of tokens * top entries")
+    _need(weight.dtype == torch.float32 and weight.numel() >= T * top and counts.dtype == torch.int32 and counts.numel() >= E,
+          "moe_route: weights or counts")
+    lib().call("slb_moe_route", _p(h), _p(w_router), _p(bias), _p(choice), _p(weight), _p(rank), _p(counts), _p(place),
+               _p(order), T, d, E, int(top), DT[h.dtype], stream if stream is not None else current_stream())
+
+
+def moe_experts(h, w_gate_up, w_down, counts, order, weight, act, y, x, top: int, activation: str = "silu",
+                stream=None) -> None:
+    """x[t] += sum over the token's choices of weight * down_e(f(gate_e h) * (up_e h)). w_gate_up [experts, 2 * ff, d]
+    (gate rows, then up rows), w_down [experts, d, ff]; act [T * top, ff] and y [T * top, d] float32 are scratch."""
+    _cuda(h, w_gate_up, w_down, counts, order, weight, act, y, x)
+    T, d = h.shape
+    E, ff2, _ = w_gate_up.shape
+    ff = ff2 // 2
+    _need(w_gate_up.shape == (E, 2 * ff, d) and w_down.shape == (E, d, ff), "moe_experts: expert matrices")
+    _need(h.dtype == w_gate_up.dtype == w_down.dtype == act.dtype and h.dtype in DT, "moe_experts: dtypes")
+    _need(act.shape == (T * top, ff) and y.shape == (T * top, d) and y.dtype == torch.float32, "moe_experts: scratch")
+    _need(x.shape == (T, d) and x.dtype == torch.float32, "moe_experts: the stream")
+    _need(activation in ACTIVATIONS, f"moe_experts: activation {activation!r}")
+    lib().call("slb_moe_experts", _p(h), _p(w_gate_up), _p(w_down), _p(counts), _p(order), _p(weight), _p(act), _p(y),
+               _p(x), T, d, ff, E, int(top), ACTIVATIONS[activation], DT[h.dtype],
+               stream if stream is not None else current_stream())

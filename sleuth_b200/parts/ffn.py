@@ -1,5 +1,5 @@
-"""Feed-forward parts. ``gated_mlp``: down(act(gate(h)) * up(h)) without biases
-(sleuth/forge/model/mlp.py:25-41). Gate and up matrices are stacked at load time into one
+"""Feed-forward parts. ``gated_mlp``: down(act(gate(h)) * up(h)) without biases, act = silu
+(sleuth/forge/model/mlp.py:25-41) or relu (product, then the gated-activation kernel). Gate and up matrices are stacked at load time into one
 ``[2 * intermediate, hidden]`` matrix, so one product feeds the activation kernel."""
 
 from __future__ import annotations
@@ -24,8 +24,9 @@ class GatedMLP(Part):
     accepts_normed = True
 
     def __init__(self, spec: GatedMLPSpec, ctx: BuildContext):
-        if spec.activation != "silu":
-            raise ValueError(f"gated_mlp: activation {spec.activation!r} is not supported (silu)")
+        if spec.activation not in ops.ACTIVATIONS:
+            raise ValueError(f"gated_mlp: activation {spec.activation!r} is not supported ({sorted(ops.ACTIVATIONS)})")
+        self.silu = spec.activation == "silu"     # the products' fused epilogues know this gate only
         self.spec, self.ctx = spec, ctx
         self.gate_up = self.down = None
 
@@ -42,7 +43,8 @@ class GatedMLP(Part):
         return self.gate_up.weight if self.gate_up is not None else None
 
     def fused_decode(self):
-        if self.ctx.dtype != torch.bfloat16 or self.gate_up is None or self.spec.intermediate % 32 or self.spec.hidden % 128:
+        if (self.ctx.dtype != torch.bfloat16 or self.gate_up is None or self.spec.intermediate % 32 or self.spec.hidden % 128
+                or not self.silu):
             return None
         return {"w_gu": self.gate_up.weight, "w_down": self.down.weight, "inter": self.spec.intermediate}
 
@@ -50,7 +52,10 @@ class GatedMLP(Part):
         T = h.shape[0]
         mark = ws.mark()
         act = ws.take((T, self.spec.intermediate), self.ctx.dtype)
-        if self.ctx.dtype == torch.bfloat16 and linear.use_skinny(T, self.spec.intermediate, self.spec.hidden):
+        if not self.silu:
+            gu = self.gate_up.forward(h, ws=ws, stream=b.stream)
+            ops.gated_act(gu, act, self.spec.activation, b.stream)
+        elif self.ctx.dtype == torch.bfloat16 and linear.use_skinny(T, self.spec.intermediate, self.spec.hidden):
             # norm in the product's prologue (when handed the stream), activation in its epilogue
             if (isinstance(h, Normed) and h.gain is not None and FUSE_NORM
                     and ops.skinny_supported(T, self.spec.intermediate, self.spec.hidden, norm=True)):

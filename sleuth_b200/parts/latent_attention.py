@@ -1,0 +1,113 @@
+"""Causal attention through low-rank latents over the paged latent cache, as a mixer part.
+
+With h the layer's normed input:
+
+* queries: c_q = RMSNorm(W_dq h) (gain ``dq_norm``), q = W_uq c_q, laid out head by head as ``plain_dim``
+  unrotated values followed by ``rot_dim`` rotated ones;
+* keys and values: W_dkv h has ``kv_rank + rot_dim`` rows; the first ``kv_rank``, RMS-normed (gain ``dkv_norm``),
+  are the token's latent c, the rest (not normed) is one rotated key part that all heads share. Head n's
+  unrotated key is W_uk[n] c and its value W_uv[n] c;
+* score = (q_plain . k_plain + q_rot . k_rot) * scale, causal softmax, the heads' outputs side by side, times
+  sigmoid(W_g h), then W_o, added into the stream.
+
+The cache keeps c and the rotated key part only (``LatentRequest``), and the per-head keys and values are never
+formed: the key up-projection is applied to the query instead (q_lat[n] = W_uk[n]^T q_plain[n], so that
+q_plain . (W_uk c) = q_lat . c), the softmax-weighted sum runs over the latents, and the value up-projection is
+applied to that sum (value[n] = W_uv[n] sum_j p_j c_j). One kernel then serves prompts, single tokens and chunks
+alike, and a token costs ``kv_rank + rot_dim`` cache values per layer whatever the number of heads.
+
+Launches of a step: the stacked down-projections (float32 result), the gate projection, ``latent_post`` (both
+norms, the key part's rotation, the cache write), the query up-projection, the per-head carry into the latent
+space (a batched library product), ``latent_attention`` (which turns the queries' rotated part as it loads them),
+the per-head value up-projection (batched library product), ``latent_gate``, the output projection.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..cache.paged import LatentRequest
+from ..kernels import ops
+from .base import BuildContext, Normed, ParamDecl, Part, build_position, register_mixer
+from .linear import Linear
+from .spec import LatentAttentionSpec
+
+
+class LatentAttention(Part):
+    def __init__(self, spec: LatentAttentionSpec, ctx: BuildContext):
+        if spec.rot_dim % 2:
+            raise ValueError(f"rot_dim {spec.rot_dim} must be even")
+        self.spec, self.ctx = spec, ctx
+        self.position = build_position(spec.position, ctx)
+        self.down = self.gate = self.uq = self.o = None
+        self.w_uk = self.w_uv_t = self.q_gain = self.c_gain = None
+
+    def declare(self):
+        s = self.spec
+        d = {"dq.weight": ParamDecl((s.q_rank, s.hidden)),
+             "dq_norm.weight": ParamDecl((s.q_rank,), "vector", init="gain"),
+             "uq.weight": ParamDecl((s.heads * (s.plain_dim + s.rot_dim), s.q_rank)),
+             "dkv.weight": ParamDecl((s.kv_rank + s.rot_dim, s.hidden)),
+             "dkv_norm.weight": ParamDecl((s.kv_rank,), "vector", init="gain"),
+             "uk.weight": ParamDecl((s.heads * s.plain_dim, s.kv_rank)),
+             "uv.weight": ParamDecl((s.heads * s.value_dim, s.kv_rank)),
+             "o.weight": ParamDecl((s.hidden, s.heads * s.value_dim))}
+        if s.output_gate:
+            d["g.weight"] = ParamDecl((s.heads * s.value_dim, s.hidden))
+        return d
+
+    def bind(self, t):
+        s, dt = self.spec, self.ctx.dtype
+        self.down = Linear(torch.cat([t["dq.weight"], t["dkv.weight"]], dim=0), dt)     # one product, float32 result
+        self.gate = Linear(t["g.weight"], dt) if s.output_gate else None
+        self.uq = Linear(t["uq.weight"], dt)
+        self.o = Linear(t["o.weight"], dt)
+        self.w_uk = t["uk.weight"].to(dt).view(s.heads, s.plain_dim, s.kv_rank).contiguous()
+        self.w_uv_t = t["uv.weight"].to(dt).view(s.heads, s.value_dim, s.kv_rank).transpose(1, 2)   # [H, rank, value]
+        self.q_gain, self.c_gain = t["dq_norm.weight"], t["dkv_norm.weight"]
+
+    def cache_request(self):
+        s = self.spec
+        return LatentRequest(s.kv_rank + s.rot_dim, s.window)
+
+    def lead_weight(self):
+        return self.down.weight if self.down is not None else None
+
+    def forward(self, h, x, b, view, ws):
+        s, dt = self.spec, self.ctx.dtype
+        if isinstance(h, Normed):
+            h = h.tensor()
+        T, H, R, P, dn, dv = h.shape[0], s.heads, s.kv_rank, s.rot_dim, s.plain_dim, s.value_dim
+        table = b.tables[view.group]
+        tables = self.position.tables()
+        cos, sin = tables if tables is not None else (None, None)
+        rotated = self.position.rot_dim
+        mark = ws.mark()
+        lat = self.down.forward(h, ws=ws, stream=b.stream, out_dtype=torch.float32)
+        g = self.gate.forward(h, ws=ws, stream=b.stream) if self.gate is not None else None
+        cq = ws.take((T, s.q_rank), dt)
+        ops.latent_post(lat, self.q_gain, self.c_gain, cos, sin, cq, view.pool if view.writes else None, b.tok_seq,
+                        b.tok_pos, table, s.q_rank, R, P, rotated, s.norm_eps, b.stream)
+        q = self.uq.forward(cq, ws=ws, stream=b.stream).view(T, H, dn + P)
+        q_lat = ws.take((H, T, R), dt)
+        torch.bmm(q[:, :, :dn].transpose(0, 1), self.w_uk, out=q_lat)
+        o_lat = ws.take((H, T, R), dt)
+        # the number of key slices follows the batch and the longest sequence allowed, never the lengths of the
+        # moment: a recorded step stays valid as its sequences grow
+        splits = ops.latent_splits(b.n, H, b.max_count, table.shape[1] * 64)
+        floats = ops.latent_scratch_floats(T, H, R, splits)
+        scratch = ws.take((floats,), torch.float32) if floats else None
+        ops.latent_attention(q_lat, q, view.pool, o_lat, cos, sin, b.seq_start, b.past, b.counts, table, b.max_count,
+                             H, R, P, dn, rotated, view.window, s.scale, splits, scratch, b.stream)
+        val = ws.take((H, T, dv), dt)
+        torch.bmm(o_lat, self.w_uv_t, out=val)
+        y = ws.take((T, H * dv), dt)
+        if g is not None:
+            ops.latent_gate(val, g, y, b.stream)
+        else:
+            y.view(T, H, dv).copy_(val.transpose(0, 1))
+        self.o.forward(y, into=x, ws=ws, stream=b.stream, next_read=getattr(b, "next_read", None))
+        ws.release(mark)
+
+
+register_mixer("latent_attention", LatentAttention)

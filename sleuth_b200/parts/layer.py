@@ -1,5 +1,7 @@
 """Arrangements of a mixer, a feed-forward and their norms in one layer.
 
+``parallel``: h = norm1(x); x += mixer(h) + ffn(h) (one norm; the feed-forward may be absent).
+
 ``prenorm``: x += mixer(norm1(x)); x += ffn(norm2(x)) (sleuth/forge/model/transformer.py:78,87-88,96,99).
 The layer owns the residual arrangement only; the parts it is given decide everything else. The sum
 itself is a float32 accumulation into the stream, done by the last product of the mixer or ffn.
@@ -65,4 +67,36 @@ class PreNormLayer(Part):
         return n if part.accepts_normed else n.tensor()
 
 
+class ParallelLayer(Part):
+    """h = norm1(x); x += mixer(h) + ffn(h): one norm, both sublayers read its output, and each adds its result into
+    the float32 stream. The feed-forward may be absent."""
+
+    def __init__(self, spec: LayerSpec, ctx: BuildContext):
+        self.ctx = ctx
+        self.norm1 = build_norm(spec.norm1, ctx)
+        self.mixer = build_mixer(spec.mixer, ctx)
+        self.ffn = build_ffn(spec.ffn, ctx) if spec.ffn is not None else None
+        self.children = {"norm1": self.norm1, "mixer": self.mixer}
+        if self.ffn is not None:
+            self.children["ffn"] = self.ffn
+        self.capturable = all(getattr(p, "capturable", True) for p in self.children.values())
+
+    declare = PreNormLayer.declare
+    bind = PreNormLayer.bind
+    cache_request = PreNormLayer.cache_request
+    lead_weight = PreNormLayer.lead_weight
+
+    def forward(self, x, b, view, ws):
+        mark = ws.mark()
+        after = getattr(b, "next_read", None)
+        h = Normed(self.norm1, x, ws, b.stream, self.ctx.dtype).tensor()
+        b.next_read = lead_weight_of(self.ffn) if self.ffn is not None else after
+        self.mixer.forward(h, x, b, view, ws)
+        b.next_read = after
+        if self.ffn is not None:
+            self.ffn.forward(h, x, b, ws)
+        ws.release(mark)
+
+
 register_layer("prenorm", PreNormLayer)
+register_layer("parallel", ParallelLayer)

@@ -1,0 +1,68 @@
+"""Routed experts as a feed-forward part.
+
+Router logits z = W_r h + b in float32 (W_r and b are kept in float32; h is the layer's normed input in the run
+dtype). A token uses the ``top`` experts with the largest logits, weighted by the softmax over those logits alone,
+and an expert is down(act(gate h) * (up h)). The part's output, the weighted sum, is added into the stream.
+
+The experts' matrices are stacked at load time ([experts, 2 * ff, hidden] for gate and up, [experts, hidden, ff]
+for down). A step runs five kernels (``csrc/moe.cu``): router and counts, the expert-ordered list of (token,
+choice) pairs, gate/up with the activation, down scaled by the pair's weight, and the sum over a token's choices
+in the order of the choices. None of them needs the host to know the counts, so the part can be recorded in a
+CUDA graph like any other.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+from .base import BuildContext, Normed, ParamDecl, Part, register_ffn
+from .spec import RoutedExpertsSpec
+
+
+class RoutedExperts(Part):
+    def __init__(self, spec: RoutedExpertsSpec, ctx: BuildContext):
+        if spec.activation not in ops.ACTIVATIONS:
+            raise ValueError(f"routed_experts: activation {spec.activation!r} is not supported ({sorted(ops.ACTIVATIONS)})")
+        if not 0 < spec.top <= spec.experts:
+            raise ValueError(f"routed_experts: top {spec.top} of {spec.experts} experts")
+        self.spec, self.ctx = spec, ctx
+        self.w_router = self.bias = self.w_gate_up = self.w_down = None
+
+    def declare(self):
+        s = self.spec
+        d = {"router.weight": ParamDecl((s.experts, s.hidden), "vector")}
+        if s.router_bias:
+            d["router.bias"] = ParamDecl((s.experts,), "vector")
+        for e in range(s.experts):
+            d[f"e{e}.gate.weight"] = ParamDecl((s.intermediate, s.hidden))
+            d[f"e{e}.up.weight"] = ParamDecl((s.intermediate, s.hidden))
+            d[f"e{e}.down.weight"] = ParamDecl((s.hidden, s.intermediate))
+        return d
+
+    def bind(self, t):
+        s, dt = self.spec, self.ctx.dtype
+        self.w_router = t["router.weight"].to(torch.float32).contiguous()
+        self.bias = t["router.bias"].to(torch.float32).contiguous() if s.router_bias else None
+        self.w_gate_up = torch.stack([torch.cat([t[f"e{e}.gate.weight"], t[f"e{e}.up.weight"]], dim=0)
+                                      for e in range(s.experts)]).to(dt).contiguous()
+        self.w_down = torch.stack([t[f"e{e}.down.weight"] for e in range(s.experts)]).to(dt).contiguous()
+
+    def forward(self, h, x, b, ws):
+        s, dt = self.spec, self.ctx.dtype
+        if isinstance(h, Normed):
+            h = h.tensor()
+        T = h.shape[0]
+        pairs = T * s.top
+        mark = ws.mark()
+        choice, rank, place, order = (ws.take((pairs,), torch.int32) for _ in range(4))
+        counts = ws.take((s.experts,), torch.int32)
+        weight = ws.take((pairs,), torch.float32)
+        act = ws.take((pairs, s.intermediate), dt)
+        y = ws.take((pairs, s.hidden), torch.float32)
+        ops.moe_route(h, self.w_router, self.bias, choice, weight, rank, counts, place, order, s.top, b.stream)
+        ops.moe_experts(h, self.w_gate_up, self.w_down, counts, order, weight, act, y, x, s.top, s.activation, b.stream)
+        ws.release(mark)
+
+
+register_ffn("routed_experts", RoutedExperts)

@@ -53,8 +53,31 @@ class AttentionSpec:
 
 
 @dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Causal attention through low-rank latents. Queries: a normed latent of ``q_rank`` values, up-projected to
+    ``heads`` x (``plain_dim`` unrotated + ``rot_dim`` rotated) values. Keys and values: one normed latent of
+    ``kv_rank`` values per token, from which each head's ``plain_dim`` key values and ``value_dim`` values are
+    up-projected, plus one rotated key part of ``rot_dim`` values shared by all heads. The cache keeps the latent
+    and the rotated part only. ``position`` rotates the ``rot_dim`` parts (its ``head_dim`` is ``rot_dim``).
+    ``output_gate``: the heads' outputs are multiplied by sigmoid(W_g h) before the output matrix."""
+    hidden: int
+    heads: int
+    plain_dim: int
+    rot_dim: int
+    value_dim: int
+    q_rank: int
+    kv_rank: int
+    position: PositionSpec
+    scale: float
+    norm_eps: float = 1e-6
+    window: int = 0              # 0 = every earlier token
+    output_gate: bool = True
+    kind: str = "latent_attention"
+
+
+@dataclass(frozen=True)
 class GatedMLPSpec:
-    """down(act(gate(x)) * up(x)), no biases."""
+    """down(act(gate(x)) * up(x)), no biases; ``activation``: "silu" or "relu"."""
     hidden: int
     intermediate: int
     activation: str = "silu"
@@ -62,8 +85,22 @@ class GatedMLPSpec:
 
 
 @dataclass(frozen=True)
+class RoutedExpertsSpec:
+    """``experts`` gated feed-forwards of ``intermediate`` channels, of which a token uses the ``top`` with the
+    largest router logits (W_r h + b, float32), weighted by the softmax over those logits alone."""
+    hidden: int
+    intermediate: int
+    experts: int
+    top: int
+    activation: str = "silu"
+    router_bias: bool = True
+    kind: str = "routed_experts"
+
+
+@dataclass(frozen=True)
 class LayerSpec:
-    """One layer: an arrangement (``kind``) of a mixer, a feed-forward and their norms.
+    """One layer: an arrangement (``kind``) of a mixer, a feed-forward and their norms. ``kind="parallel"`` has one
+    norm (``norm2`` is None) and may have no feed-forward (``ffn`` is None).
 
     ``names`` maps each part-local tensor name ("norm1.weight", "mixer.q_proj.weight",
     "ffn.down.weight", ...) to its name in the weight files."""
@@ -78,9 +115,14 @@ class LayerSpec:
 @dataclass(frozen=True)
 class ScheduleEntry:
     """One application of a layer. ``cache`` numbers the cache entry it uses; the first application
-    in schedule order that names an entry owns it (and writes it), later ones only read it."""
+    in schedule order that names an entry owns it (and writes it), later ones only read it.
+
+    Right before the application the model may add to the stream: the embedding's output once more
+    (``add_embedding``) and row ``add_row`` of the model's table of pass vectors (``ModelSpec.pass_rows``)."""
     layer: int
     cache: int
+    add_embedding: bool = False
+    add_row: int = -1
 
 
 @dataclass(frozen=True)
@@ -117,6 +159,8 @@ class ModelSpec:
     head: HeadSpec
     max_positions: int
     ignored_tensors: tuple = ()   # regular expressions of tensor names a checkpoint may hold and nobody reads
+    pass_rows: str | None = None  # checkpoint name of a [rows, width] table whose rows schedule entries add to the stream
+    pass_rows_count: int = 0
 
     def __post_init__(self):
         seen = set()
@@ -124,8 +168,31 @@ class ModelSpec:
             if not 0 <= e.layer < len(self.layers):
                 raise ValueError(f"schedule names layer {e.layer}, the model has {len(self.layers)}")
             seen.add(e.cache)
+            if e.add_row >= 0 and not (self.pass_rows and e.add_row < self.pass_rows_count):
+                raise ValueError(f"schedule adds row {e.add_row} of a table of {self.pass_rows_count} pass vectors")
         if seen and seen != set(range(len(seen))):
             raise ValueError(f"cache entries must be numbered 0..{len(seen) - 1} without gaps, got {sorted(seen)}")
+
+
+def looped_schedule(n_layers: int, start: int, stop: int, times: int) -> tuple:
+    """Layers ``start .. stop - 1`` run ``times`` times in a row with the same weights, each pass with cache entries of
+    its own; every pass begins by adding its row of the pass vectors, and every pass but the first adds the
+    embedding's output before that. The other layers run once."""
+    if not (0 <= start < stop <= n_layers and times >= 1):
+        raise ValueError(f"a loop over layers {start}..{stop - 1}, {times} times, does not fit {n_layers} layers")
+    out, cache = [], 0
+    for i in range(start):
+        out.append(ScheduleEntry(i, cache))
+        cache += 1
+    for t in range(times):
+        for i in range(start, stop):
+            first = i == start
+            out.append(ScheduleEntry(i, cache, add_embedding=first and t > 0, add_row=t if first else -1))
+            cache += 1
+    for i in range(stop, n_layers):
+        out.append(ScheduleEntry(i, cache))
+        cache += 1
+    return tuple(out)
 
 
 def straight_schedule(n_layers: int) -> tuple:
