@@ -525,6 +525,106 @@ def run_reference(args) -> dict:
     }
 
 
+# ------------------------------------------------------------------ another design beside the closest one ----
+
+def lezepel_config(width, layers, heads, dim, rot, vdim, q_rank, kv_rank, experts, top, ff, vocab=32768) -> dict:
+    mixer = {"heads": heads, "dim": dim, "rot_dim": rot, "vdim": vdim, "q_rank": q_rank, "kv_rank": kv_rank,
+             "scale": (dim + rot) ** -0.5, "rot": {"base": 10000.0, "dims": rot}}
+    moe = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top}}
+    block = [{"type": "latent_attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": top * ff}}]
+    block += [{"type": "latent_attention", "mixer": mixer, "mlp": moe} for _ in range(layers - 1)]
+    return {"architecture": "Lezepel", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
+            "layers": block, "loop": {"start": 1, "stop": 2, "times": 1}}
+
+
+def qwen3_like(width, layers, heads, head_dim, inter, vocab=32768) -> dict:
+    return dict(CONFIG, vocab_size=vocab, hidden_size=width, num_hidden_layers=layers, num_attention_heads=heads,
+                num_key_value_heads=max(1, heads // 2), head_dim=head_dim, intermediate_size=inter, tie_word_embeddings=False)
+
+
+# Layer sizes after published models of the family: width 1,024 with 16 heads, and width 2,048 with 16 heads of 128 + 64,
+# a latent of 512 and 64 experts of 1,408 channels of which 6 are used. The closest existing model has the same width
+# and layer count, heads of the same total width and a feed-forward as wide as the experts a token uses.
+DESIGN_SIZES = {
+    "w1024": (dict(width=1024, layers=8, heads=16, dim=64, rot=32, vdim=64, q_rank=384, kv_rank=256, experts=16, top=4, ff=768),
+              dict(width=1024, layers=8, heads=16, head_dim=64, inter=3072)),
+    "w2048": (dict(width=2048, layers=6, heads=16, dim=128, rot=64, vdim=128, q_rank=768, kv_rank=512, experts=64, top=6, ff=1408),
+              dict(width=2048, layers=6, heads=16, head_dim=128, inter=8448)),
+}
+
+
+def design_point(config: dict, prompt_len: int, batches, steps: int, warmup: int) -> dict:
+    """Prefill of one prompt and decode steps at some batch sizes for one random-weight model, device-timed, plus the
+    device time of each of this library's launchers in one un-recorded prompt step and one decode step."""
+    import numpy as np
+    import torch
+
+    from sleuth_b200.engine.engine import Engine
+    from sleuth_b200.kernels import ops
+    big = max(batches)
+    eng = Engine.from_config(config, seed=1, dtype="bf16", max_seq_len=prompt_len + steps + warmup + 64,
+                             max_tokens=big * (prompt_len + steps + warmup + 128))
+    rng = np.random.default_rng(0)
+    V = eng.vocab
+    out = {"weights_mb": round(eng.model.weight_bytes() / 1e6, 1), "cache_bytes_per_token": eng.cache.nbytes() // (eng.cache.n_pages * 64)}
+    prompt = rng.integers(0, V, size=prompt_len).tolist()
+    times = []
+    for i in range(warmup + 5):
+        slots = eng.open(1)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        eng.prefill(slots, [prompt])
+        b.record()
+        torch.cuda.synchronize()
+        eng.close(slots)
+        if i >= warmup:
+            times.append(a.elapsed_time(b))
+    out["prefill_ms"] = round(statistics.median(times), 3)
+    out["prefill_tok_s"] = round(prompt_len / out["prefill_ms"] * 1e3)
+    for batch in batches:
+        ms, _, ctx = decode_run(eng, batch, steps, warmup, 3, None, prompt_len)
+        out[f"decode_b{batch}_ms"] = round(ms, 4)
+        out[f"decode_b{batch}_tok_s"] = round(batch / ms * 1e3)
+    # where the time goes, launcher by launcher (graphs off so that every launch is seen; cuBLAS products are not)
+    eng.stepper.use_graphs = False
+    lib = ops.lib()
+    for label, count in (("prompt", prompt_len), ("token", 1)):
+        slots = eng.open(8 if count == 1 else 1)
+        if count == 1:
+            eng.prefill(slots, [prompt] * 8)
+        torch.cuda.synchronize()
+        lib.start_timing()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        if count == 1:
+            eng.decode(slots, [1] * 8)
+        else:
+            eng.prefill(slots, [prompt])
+        b.record()
+        t = lib.stop_timing()
+        out[f"launchers_{label}_us"] = {k: [n, round(ms * 1e3, 1)] for k, (n, ms) in sorted(t.items())}
+        out[f"launchers_{label}_step_ms"] = round(a.elapsed_time(b), 3)
+        eng.close(slots)
+    release(eng)
+    return out
+
+
+def run_design(args) -> dict:
+    """``--design lezepel``: the Lezepel design beside the closest existing model (the Qwen3 dense decoder) at equal
+    width, depth and active feed-forward width, random weights, bfloat16: prompt and decode throughput and where the
+    time goes. The default workload of this file does not change."""
+    out = {"design": args.design, "dtype": "bf16", "data": "synthetic", "prompt": args.design_prompt, "sizes": {}}
+    for name, (mine, theirs) in DESIGN_SIZES.items():
+        if args.design_size not in ("all", name):
+            continue
+        out["sizes"][name] = {
+            "lezepel": design_point(lezepel_config(**mine), args.design_prompt, (1, 8), args.design_steps, max(3, args.warmup)),
+            "qwen3": design_point(qwen3_like(**theirs), args.design_prompt, (1, 8), args.design_steps, max(3, args.warmup)),
+        }
+    return out
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -539,6 +639,11 @@ def main() -> int:
     ap.add_argument("--skip-other-configs", action="store_true",
                     help="leave out the 32-bit block and the 4B- and 8B-shaped points (a quicker run)")
     ap.add_argument("--layers5", type=int, default=0, help="layers of the 8B-shaped point (0 = all 36)")
+    ap.add_argument("--design", choices=["lezepel"], default=None,
+                    help="instead of the default workload: this design beside the closest existing model at equal size")
+    ap.add_argument("--design-size", default="all", help="one of the sizes of --design (w1024, w2048) or all")
+    ap.add_argument("--design-prompt", type=int, default=2048)
+    ap.add_argument("--design-steps", type=int, default=64)
     args = ap.parse_args()
     if args.print_config:
         print(json.dumps(CONFIG))
@@ -548,6 +653,9 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.design:
+        print(json.dumps(run_design(args)))
+        return 0
     if args.only != "all" and args.impl == "ours":
         out = run_part(args)
     else:

@@ -42,6 +42,22 @@ def model_folders(tmp_path_factory):
     return out
 
 
+@pytest.fixture(scope="session")
+def lezepel_folders(tmp_path_factory):
+    """Model folders of the tiny Lezepel configurations, float32 weights, made once per session."""
+    import torch
+
+    import tiny_lezepel
+    from sleuth_b200.weights.random_init import write_random_model
+    out = {}
+    for name, cfg in tiny_lezepel.CONFIGS.items():
+        d = tmp_path_factory.mktemp(f"lezepel_{name}")
+        write_random_model(d, cfg, seed=tiny_lezepel.SEEDS[name], dtype=torch.float32, std=tiny_lezepel.STD)
+        tiny_lezepel.spread_router_biases(d)
+        out[name] = str(d)
+    return out
+
+
 def pytest_terminal_summary(terminalreporter):
     """The largest differences from the plain implementation that the GPU tests saw (tests/closeness.py)."""
     import closeness
