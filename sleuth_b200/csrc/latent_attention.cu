@@ -12,8 +12,9 @@
 //   latent_attn_kernel    causal softmax attention of all heads of a tile of tokens over the cache rows, float32
 //                         arithmetic; the rotation of the query's rotated part happens as the queries are loaded;
 //                         a long sequence's keys may be cut into slices whose partial results latent_merge_kernel joins
+//   latent_attn_mma_kernel  the same on the warp-level tensor cores (bfloat16, widths that are multiples of 16)
 //   latent_gate_kernel    y[t, h, :] = value[h, t, :] * sigmoid(g[t, h, :])
-#include "common.cuh"
+#include "mma_sync.cuh"
 
 namespace slb {
 
@@ -275,6 +276,205 @@ __global__ void __launch_bounds__(kLatWarps * 32) latent_attn_kernel(const Laten
   }
 }
 
+// The same attention on the warp-level tensor cores, for bfloat16 and widths that are multiples of 16.
+// Block: 64 (token, head) rows on four warps, 16 rows a warp, so that a row's softmax stays inside its warp. Queries
+// (latent part and rotated part, turned as they are loaded) and one chunk of 64 cache rows lie in shared memory as
+// bfloat16 with rows padded by 16 bytes, which keeps ldmatrix free of bank conflicts. Scores = Q K^T over all W
+// columns (mma.sync m16n8k16, float32 sums), online softmax in registers, then P times the chunk's first columns, read
+// from the same shared rows through transposing loads. A block takes at most NTM * 16 value columns (its sums live in
+// registers); a wider latent is shared by several blocks (grid z), each of which forms the scores again.
+template <int NTM>
+__global__ void __launch_bounds__(128) latent_attn_mma_kernel(const LatentAttnArgs a, int nt16, int groups) {
+  pdl_enter();
+  extern __shared__ __align__(16) unsigned char lat_raw[];
+  const int W = a.R + a.P, ks = a.kstride;
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(lat_raw);     // [64][ks]
+  __nv_bfloat16* Ks = Qs + 64 * ks;                                  // [64][ks]
+  const int seq = blockIdx.y;
+  int z = blockIdx.z;
+  const int slice = z % a.splits;
+  z /= a.splits;
+  const int grp = z % groups, hc = z / groups;
+  const int count = a.counts[seq], past = a.past[seq];
+  const int t0 = blockIdx.x * a.tq;
+  if (t0 >= count) return;
+  const int nt = min(a.tq, count - t0);
+  const int h0 = hc * a.hb, nh = min(a.hb, a.H - h0);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
+  const __nv_bfloat16* q_lat = (const __nv_bfloat16*)a.q_lat;
+  const __nv_bfloat16* q_raw = (const __nv_bfloat16*)a.q_raw;
+  const __nv_bfloat16* pool = (const __nv_bfloat16*)a.pool;
+  const int tok0 = a.seq_start[seq] + t0;
+  const int half = a.rot / 2;
+  for (int r = warp; r < 64; r += 4) {
+    const int tq = r / a.hb, hh = r % a.hb;
+    __nv_bfloat16* qs = Qs + (size_t)r * ks;
+    if (!(tq < nt && hh < nh)) {
+      for (int i = lane; i < W; i += 32) qs[i] = __float2bfloat16_rn(0.f);
+      continue;
+    }
+    const int tok = tok0 + tq, h = h0 + hh, pos = past + t0 + tq;
+    const __nv_bfloat16* ql = q_lat + ((size_t)h * a.T + tok) * a.R;
+    for (int i = lane; i < a.R; i += 32) qs[i] = ql[i];
+    const __nv_bfloat16* qr = q_raw + ((size_t)tok * a.H + h) * (a.dn + a.P) + a.dn;
+    for (int i = lane; i < a.P; i += 32) {
+      float v = __bfloat162float(qr[i]);
+      if (i < a.rot) {
+        const int f = i < half ? i : i - half;
+        const float c = a.cos_t[(size_t)pos * half + f], sn = a.sin_t[(size_t)pos * half + f];
+        v = i < half ? v * c - __bfloat162float(qr[i + half]) * sn : v * c + __bfloat162float(qr[i - half]) * sn;
+      }
+      qs[a.R + i] = __float2bfloat16_rn(v);
+    }
+  }
+  int pos_r[2], lo_r[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int row = warp * 16 + g + 8 * h;
+    const int tq = row / a.hb, hh = row % a.hb;
+    pos_r[h] = (tq < nt && hh < nh) ? past + t0 + tq : -1;
+    lo_r[h] = a.window > 0 ? max(0, pos_r[h] - a.window + 1) : 0;
+  }
+  const bool warp_active = __any_sync(0xffffffffu, pos_r[0] >= 0 || pos_r[1] >= 0);
+  const int last_pos = past + t0 + nt - 1;
+  int key_lo = a.window > 0 ? max(0, past + t0 - a.window + 1) : 0;
+  key_lo = key_lo / 64 * 64;
+  const int n_chunks = (last_pos - key_lo) / 64 + 1;
+  const int per = (n_chunks + a.splits - 1) / a.splits;
+  const int c_lo = slice * per, c_hi = min(n_chunks, c_lo + per);
+  const int* trow = a.table + (size_t)seq * a.stride;
+  const int col0 = grp * nt16 * 16;
+  const float scale_log2 = a.scale * 1.4426950408889634f;
+
+  float o[2 * NTM][4];
+#pragma unroll
+  for (int i = 0; i < 2 * NTM; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m_r[2] = {-INFINITY, -INFINITY}, l_r[2] = {0.f, 0.f};
+  const uint32_t q_base = smem_u32(Qs), k_base = smem_u32(Ks);
+  const int pieces = W / 8;
+
+  for (int c = c_lo; c < c_hi; ++c) {
+    const int k0 = key_lo + c * 64;
+    const int nk = min(64, last_pos - k0 + 1);
+    __syncthreads();
+    {
+      const __nv_bfloat16* src = pool + (size_t)trow[k0 / kPageTokens] * kPageTokens * W;
+      for (int i = tid; i < 64 * pieces; i += 128) {
+        const int j = i / pieces, p8 = (i - j * pieces) * 8;
+        __nv_bfloat16* dst = Ks + (size_t)j * ks + p8;
+        if (j < nk) cp_async16(smem_u32(dst), src + (size_t)j * W + p8);
+        else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);      // rows past the sequence: zeros, never stale values
+      }
+      cp_async_commit();
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    if (!warp_active) continue;
+    float s[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+    for (int kb = 0; kb < W / 16; ++kb) {
+      uint32_t qf[4];
+      ldmatrix_x4(qf, q_base + 2 * ((warp * 16 + (lane & 15)) * ks + kb * 16 + ((lane >> 4) << 3)));
+#pragma unroll
+      for (int jp = 0; jp < 4; ++jp) {
+        uint32_t kf[4];
+        ldmatrix_x4(kf, k_base + 2 * ((jp * 16 + (lane & 7) + ((lane >> 4) << 3)) * ks + kb * 16 + (((lane >> 3) & 1) << 3)));
+        mma_bf16(s[2 * jp], qf, kf[0], kf[1]);
+        mma_bf16(s[2 * jp + 1], qf, kf[2], kf[3]);
+      }
+    }
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int h = e >> 1;
+        const int key = k0 + j * 8 + 2 * t4 + (e & 1);
+        float v = s[j][e] * scale_log2;
+        if (key > pos_r[h] || key < lo_r[h]) v = -INFINITY;
+        s[j][e] = v;
+        mx[h] = fmaxf(mx[h], v);
+      }
+    }
+    float alpha[2], m_use[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+      mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+      const float m_new = fmaxf(m_r[h], mx[h]);
+      m_use[h] = m_new == -INFINITY ? 0.f : m_new;
+      alpha[h] = exp2f(m_r[h] - m_use[h]);
+      m_r[h] = m_new;
+    }
+    float sum[2] = {0.f, 0.f};
+    uint32_t pf[4][4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float p0 = exp2f(s[j][0] - m_use[0]), p1 = exp2f(s[j][1] - m_use[0]);
+      const float p2 = exp2f(s[j][2] - m_use[1]), p3 = exp2f(s[j][3] - m_use[1]);
+      sum[0] += p0 + p1;
+      sum[1] += p2 + p3;
+      pf[j >> 1][(j & 1) * 2 + 0] = pack_bf16(p0, p1);
+      pf[j >> 1][(j & 1) * 2 + 1] = pack_bf16(p2, p3);
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) l_r[h] = l_r[h] * alpha[h] + sum[h];
+#pragma unroll
+    for (int i = 0; i < 2 * NTM; ++i) {
+      o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
+      o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+    }
+#pragma unroll
+    for (int kb = 0; kb < 4; ++kb) {
+#pragma unroll
+      for (int dp = 0; dp < NTM; ++dp) {
+        if (dp < nt16 && col0 + dp * 16 < a.R) {
+          uint32_t vf[4];
+          ldmatrix_x4_trans(vf, k_base + 2 * ((kb * 16 + (lane & 15)) * ks + col0 + dp * 16 + ((lane >> 4) << 3)));
+          mma_bf16(o[2 * dp], pf[kb], vf[0], vf[1]);
+          mma_bf16(o[2 * dp + 1], pf[kb], vf[2], vf[3]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    l_r[h] += __shfl_xor_sync(0xffffffffu, l_r[h], 1);
+    l_r[h] += __shfl_xor_sync(0xffffffffu, l_r[h], 2);
+  }
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    if (pos_r[h] < 0) continue;
+    const int row = warp * 16 + g + 8 * h;
+    const int tok = tok0 + row / a.hb, head = h0 + row % a.hb;
+    if (a.splits == 1) {
+      const float inv = l_r[h] > 0.f ? 1.0f / l_r[h] : 0.f;
+      __nv_bfloat16* dst = (__nv_bfloat16*)a.out + ((size_t)head * a.T + tok) * a.R;
+#pragma unroll
+      for (int i = 0; i < 2 * NTM; ++i) {
+        const int col = col0 + i * 8 + 2 * t4;
+        if ((i >> 1) < nt16 && col < a.R)
+          *reinterpret_cast<uint32_t*>(dst + col) = pack_bf16(o[i][2 * h] * inv, o[i][2 * h + 1] * inv);
+      }
+    } else {
+      float* dst = a.parts + ((size_t)slice * a.T * a.H + (size_t)tok * a.H + head) * (a.R + 2);
+#pragma unroll
+      for (int i = 0; i < 2 * NTM; ++i) {
+        const int col = col0 + i * 8 + 2 * t4;
+        if ((i >> 1) < nt16 && col < a.R) {
+          dst[col] = o[i][2 * h];
+          dst[col + 1] = o[i][2 * h + 1];
+        }
+      }
+      if (grp == 0 && t4 == 0) {
+        dst[a.R] = m_r[h] == -INFINITY ? -INFINITY : m_r[h] * 0.6931471805599453f;      // the merge works with e, not 2
+        dst[a.R + 1] = l_r[h];
+      }
+    }
+  }
+}
+
 // One warp per (token, head): joins the slices in slice order.
 template <typename T>
 __global__ void latent_merge_kernel(const float* __restrict__ parts, T* __restrict__ out, int rows, int Tn, int H, int R,
@@ -365,6 +565,13 @@ extern "C" int slb_latent_attention_supported(int R, int P) {
   return R > 0 && P >= 0 && lat_rv(R) > 0 && lat_chunk_for(R + P, kstride, bytes) > 0 ? 1 : 0;
 }
 
+// Tests set this to compare the tensor-core kernel with the general one on the same inputs.
+static int slb_latent_force_generic = 0;
+extern "C" int slb_latent_attention_general_only(int on) {
+  slb_latent_force_generic = on;
+  return 0;
+}
+
 extern "C" int slb_latent_attention(const void* q_lat, const void* q_raw, const void* pool, void* out, float* parts,
                                     const float* cos_t, const float* sin_t, const int* seq_start, const int* past,
                                     const int* counts, const int* table, int stride, int n_seqs, int max_count, int T,
@@ -380,6 +587,38 @@ extern "C" int slb_latent_attention(const void* q_lat, const void* q_raw, const 
   a.q_lat = q_lat; a.q_raw = q_raw; a.pool = pool; a.out = out; a.parts = parts; a.cos_t = cos_t; a.sin_t = sin_t;
   a.seq_start = seq_start; a.past = past; a.counts = counts; a.table = table; a.stride = stride; a.T = T; a.H = H;
   a.R = R; a.P = P; a.dn = dn; a.rot = rot; a.window = window; a.splits = splits; a.scale = scale;
+  cudaStream_t s = (cudaStream_t)stream;
+  const bool aligned = ((uintptr_t)q_lat | (uintptr_t)q_raw | (uintptr_t)pool | (uintptr_t)out) % 16 == 0;
+  if (dtype == kBF16 && R % 16 == 0 && (R + P) % 16 == 0 && aligned && (size_t)128 * (R + P + 8) * 2 <= 200 * 1024 &&
+      !slb_latent_force_generic) {
+    const int tiles16 = R / 16;
+    const int groups = (tiles16 + 15) / 16;
+    const int nt16 = (tiles16 + groups - 1) / groups;
+    a.chunk = 64;
+    a.kstride = R + P + 8;
+    a.hb = H < 64 ? H : 64;
+    a.tq = 64 / a.hb;
+    const int head_chunks = (H + a.hb - 1) / a.hb;
+    const size_t smem = (size_t)128 * a.kstride * 2;
+    const dim3 grid((max_count + a.tq - 1) / a.tq, n_seqs, head_chunks * groups * splits), block(128);
+#define SLB_LATM(V)                                                                                              \
+  do {                                                                                                           \
+    static bool raised = false;                                                                                  \
+    if (!raised) {                                                                                               \
+      cudaFuncSetAttribute(latent_attn_mma_kernel<V>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);  \
+      raised = true;                                                                                             \
+    }                                                                                                            \
+    launch(latent_attn_mma_kernel<V>, grid, block, smem, s, a, nt16, groups);                                    \
+  } while (0)
+    if (nt16 <= 4) SLB_LATM(4); else if (nt16 <= 8) SLB_LATM(8); else SLB_LATM(16);
+#undef SLB_LATM
+    int rc = check_launch("latent_attention");
+    if (rc || splits == 1) return rc;
+    const int rows = T * H;
+    launch(latent_merge_kernel<__nv_bfloat16>, dim3((rows + 7) / 8), dim3(256), 0, s, (const float*)parts,
+           (__nv_bfloat16*)out, rows, T, H, R, splits);
+    return check_launch("latent_merge");
+  }
   size_t bytes;
   a.chunk = lat_chunk_for(R + P, a.kstride, bytes);
   const int rv = lat_rv(R);
@@ -388,7 +627,6 @@ extern "C" int slb_latent_attention(const void* q_lat, const void* q_raw, const 
   a.tq = kLatRows / a.hb;
   const int head_chunks = (H + a.hb - 1) / a.hb;
   const dim3 grid((max_count + a.tq - 1) / a.tq, n_seqs, head_chunks * splits), block(kLatWarps * 32);
-  cudaStream_t s = (cudaStream_t)stream;
 #define SLB_LAT(TT, V)                                                                                   \
   do {                                                                                                   \
     static bool raised_##V = false;                                                                      \

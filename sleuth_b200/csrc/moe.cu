@@ -11,7 +11,9 @@
 //   moe_gate_up_kernel   act[place, j] = f(gate_e[j] . h) * (up_e[j] . h), f = silu or relu
 //   moe_down_kernel      y[pair, :] = weight[pair] * (down_e act[place])   (float32)
 //   moe_combine_kernel   x[t, :] += sum over the token's choices of y, in the order of the choices
-#include "common.cuh"
+// In bfloat16 with inner sizes that are multiples of 8 the two products run on the tensor cores (moe_mma_kernel);
+// the kernels above then serve float32 and odd sizes.
+#include "mma_sync.cuh"
 
 namespace slb {
 
@@ -91,16 +93,17 @@ __global__ void moe_group_kernel(const int* __restrict__ choice, const int* __re
   }
 }
 
-// Which expert and which of its row tiles block `b` takes; false when the counts leave it nothing.
-__device__ __forceinline__ bool moe_find_tile(const int* counts, int E, int b, int& expert, int& row0, int& rows) {
+// Which expert and which of its row tiles (of `tile` rows) block `b` takes; false when the counts leave it nothing.
+__device__ __forceinline__ bool moe_find_tile(const int* counts, int E, int b, int& expert, int& row0, int& rows,
+                                              int tile = kMoeTile) {
   int first = 0;
   for (int e = 0; e < E; ++e) {
     const int c = counts[e];
-    const int tiles = (c + kMoeTile - 1) / kMoeTile;
+    const int tiles = (c + tile - 1) / tile;
     if (b < tiles) {
       expert = e;
-      row0 = first + b * kMoeTile;
-      rows = min(kMoeTile, c - b * kMoeTile);
+      row0 = first + b * tile;
+      rows = min(tile, c - b * tile);
       return true;
     }
     b -= tiles;
@@ -216,6 +219,116 @@ __global__ void __launch_bounds__(256) moe_down_kernel(const T* __restrict__ act
   }
 }
 
+// ---- the same two products on the warp-level tensor cores (bfloat16, inner sizes that are multiples of 8) ----
+// A block of four warps takes 64 rows x 128 columns; a warp 16 rows x all columns (mma.sync m16n8k16, float32 sums).
+// The inner dimension goes through shared memory 32 values at a time, two buffers filled by 16-byte asynchronous
+// copies; rows are padded to 40 values, which keeps ldmatrix free of bank conflicts. GATED: the 128 columns are 64
+// gate rows and the 64 up rows that belong to them, so that a thread holds both halves of each of its outputs.
+constexpr int kMmaRows = 64, kMmaCols = 128, kMmaK = 32, kMmaPad = 40;
+
+template <bool GATED>
+__global__ void __launch_bounds__(128) moe_mma_kernel(const __nv_bfloat16* __restrict__ a_rows, const __nv_bfloat16* __restrict__ w,
+                                                      const int* __restrict__ counts, const int* __restrict__ list,
+                                                      const float* __restrict__ weight, __nv_bfloat16* __restrict__ act,
+                                                      float* __restrict__ y, int E, int top, int K, int N, int relu) {
+  pdl_enter();
+  __shared__ __align__(16) __nv_bfloat16 As[2][kMmaRows * kMmaPad];
+  __shared__ __align__(16) __nv_bfloat16 Bs[2][kMmaCols * kMmaPad];
+  __shared__ int src_row[kMmaRows];
+  int expert, row0, rows;
+  if (!moe_find_tile(counts, E, blockIdx.x, expert, row0, rows, kMmaRows)) return;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
+  // GATED: N = ff, the block's columns are gate rows n0 .. n0 + 63 and up rows N + n0 .. ; A rows are token rows of h.
+  // else:  N = the output width, columns n0 .. n0 + 127; A rows are the expert-ordered rows of act.
+  const int n0 = blockIdx.y * (GATED ? 64 : kMmaCols);
+  const int ncols = min(GATED ? 64 : kMmaCols, N - n0);
+  if (tid < kMmaRows) src_row[tid] = tid < rows ? (GATED ? list[row0 + tid] / top : row0 + tid) : -1;
+  __syncthreads();
+  const __nv_bfloat16* wb = w + (size_t)expert * (GATED ? 2 : 1) * N * K;
+
+  auto load = [&](int stage, int k0) {
+    // 64 rows x 4 sixteen-byte pieces of A, 128 rows x 4 of B
+    for (int i = tid; i < kMmaRows * 4; i += 128) {
+      const int r = i >> 2, c = (i & 3) * 8;
+      __nv_bfloat16* dst = &As[stage][r * kMmaPad + c];
+      if (src_row[r] >= 0 && k0 + c < K) cp_async16(smem_u32(dst), a_rows + (size_t)src_row[r] * K + k0 + c);
+      else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+    }
+    for (int i = tid; i < kMmaCols * 4; i += 128) {
+      const int r = i >> 2, c = (i & 3) * 8;
+      __nv_bfloat16* dst = &Bs[stage][r * kMmaPad + c];
+      int col;      // the weight row behind tile column r
+      if (GATED) col = (r & 63) < ncols ? (r < 64 ? 0 : N) + n0 + (r & 63) : -1;
+      else col = r < ncols ? n0 + r : -1;
+      if (col >= 0 && k0 + c < K) cp_async16(smem_u32(dst), wb + (size_t)col * K + k0 + c);
+      else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+    }
+    cp_async_commit();
+  };
+
+  float acc[16][4];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+  const int steps = (K + kMmaK - 1) / kMmaK;
+  load(0, 0);
+  for (int s = 0; s < steps; ++s) {
+    const int stage = s & 1;
+    if (s + 1 < steps) {
+      load(stage ^ 1, (s + 1) * kMmaK);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const uint32_t a_base = smem_u32(&As[stage][0]), b_base = smem_u32(&Bs[stage][0]);
+#pragma unroll
+    for (int kb = 0; kb < kMmaK / 16; ++kb) {
+      uint32_t af[4];
+      ldmatrix_x4(af, a_base + 2 * ((warp * 16 + (lane & 15)) * kMmaPad + kb * 16 + ((lane >> 4) << 3)));
+#pragma unroll
+      for (int jp = 0; jp < 8; ++jp) {       // 16 columns at a time
+        uint32_t bf[4];
+        ldmatrix_x4(bf, b_base + 2 * ((jp * 16 + (lane & 7) + ((lane >> 4) << 3)) * kMmaPad + kb * 16 + (((lane >> 3) & 1) << 3)));
+        mma_bf16(acc[2 * jp], af, bf[0], bf[1]);
+        mma_bf16(acc[2 * jp + 1], af, bf[2], bf[3]);
+      }
+    }
+    __syncthreads();
+  }
+  // a thread holds rows g and g + 8 of its warp, columns j * 8 + 2 * t4 (+1) of every column tile j
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int r = warp * 16 + g + 8 * half;
+    if (r >= rows) continue;
+    if (GATED) {
+      __nv_bfloat16* dst = act + (size_t)(row0 + r) * N + n0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int c = j * 8 + 2 * t4 + e;
+          if (c >= ncols) continue;
+          const float gv = acc[j][2 * half + e], uv = acc[j + 8][2 * half + e];
+          const float f = relu ? fmaxf(gv, 0.f) : gv / (1.0f + expf(-gv));
+          dst[c] = __float2bfloat16_rn(f * uv);
+        }
+      }
+    } else {
+      const int pair = list[row0 + r];
+      const float wt = weight[pair];
+      float* dst = y + (size_t)pair * N + n0;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int c = j * 8 + 2 * t4 + e;
+          if (c < ncols) dst[c] = wt * acc[j][2 * half + e];
+        }
+      }
+    }
+  }
+}
+
 __global__ void moe_combine_kernel(float* __restrict__ x, const float* __restrict__ y, int top, int dim, size_t total) {
   pdl_enter();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -277,7 +390,15 @@ extern "C" int slb_moe_experts(const void* h, const void* w_gu, const void* w_do
   SLB_REQUIRE(tiles < (1LL << 31), "moe_experts: too many pairs (%lld)", pairs);
   const dim3 block(256);
   const dim3 g1((unsigned)tiles, (ff + 31) / 32), g2((unsigned)tiles, (dim + kMoeCols - 1) / kMoeCols);
-  if (dtype == kF32) {
+  const bool aligned = ((uintptr_t)h | (uintptr_t)w_gu | (uintptr_t)w_down | (uintptr_t)act) % 16 == 0;
+  if (dtype == kBF16 && dim % 8 == 0 && ff % 8 == 0 && aligned) {
+    const long long tiles64 = pairs / kMmaRows + (pairs < E ? pairs : E);
+    launch(moe_mma_kernel<true>, dim3((unsigned)tiles64, (ff + 63) / 64), dim3(128), 0, s, (const __nv_bfloat16*)h,
+           (const __nv_bfloat16*)w_gu, counts, list, weight, (__nv_bfloat16*)act, (float*)nullptr, E, top, dim, ff, relu);
+    launch(moe_mma_kernel<false>, dim3((unsigned)tiles64, (dim + kMmaCols - 1) / kMmaCols), dim3(128), 0, s,
+           (const __nv_bfloat16*)act, (const __nv_bfloat16*)w_down, counts, list, weight, (__nv_bfloat16*)nullptr, y, E, top, ff,
+           dim, relu);
+  } else if (dtype == kF32) {
     launch(moe_gate_up_kernel<float>, g1, block, 0, s, (const float*)h, (const float*)w_gu, counts, list, (float*)act, E, top, dim, ff, relu);
     launch(moe_down_kernel<float>, g2, block, 0, s, (const float*)act, (const float*)w_down, counts, list, weight, y, E, dim, ff);
   } else {

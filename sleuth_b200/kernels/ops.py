@@ -693,6 +693,11 @@ def latent_attention_supported(rank: int, rot_dim: int) -> bool:
     return bool(fn(int(rank), int(rot_dim)))
 
 
+def latent_attention_general_only(on: bool) -> None:
+    """Send bfloat16 steps through the general kernel too (tests compare it with the tensor-core kernel)."""
+    lib().dll.slb_latent_attention_general_only(ctypes.c_int(1 if on else 0))
+
+
 def latent_splits(n_seqs: int, heads: int, max_count: int, max_len: int, sms: int | None = None) -> int:
     """Into how many slices the keys of a step are cut: none while the step's own blocks fill the SMs, else as many
     as it takes to give every SM about two blocks, each slice at least four pages long."""

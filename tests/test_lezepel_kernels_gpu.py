@@ -135,14 +135,15 @@ def run_latent_attention(H, dn, P, dv, R, pasts, counts, dtype, seed, loud=(), s
 
 @pytest.mark.parametrize("dtype", ["fp32", "bf16"])
 @pytest.mark.parametrize("H, dn, P, dv, R", [(3, 16, 8, 24, 40), (8, 64, 32, 64, 96), (1, 8, 4, 8, 7), (40, 8, 4, 8, 28),
-                                             (5, 16, 64, 16, 520)])
+                                             (5, 16, 64, 16, 520), (70, 8, 16, 8, 32), (5, 16, 64, 16, 512), (2, 8, 16, 8, 272)])
 def test_attention_over_the_latent_cache_prompts(H, dn, P, dv, R, dtype):
     got, want = run_latent_attention(H, dn, P, dv, R, pasts=[0, 0, 0, 0], counts=[1, 65, 130, 17], dtype=dtype, seed=H)
     torch.testing.assert_close(got, want, **TOL[dtype])
 
 
+@pytest.mark.parametrize("R, P", [(24, 8), (32, 16)])       # the second pair goes to the tensor-core kernel in bfloat16
 @pytest.mark.parametrize("dtype", ["fp32", "bf16"])
-def test_attention_finds_far_keys_and_keys_at_page_borders(dtype):
+def test_attention_finds_far_keys_and_keys_at_page_borders(dtype, R, P):
     """One key stands out for each chosen query: the first token, the last row of a page, the first row of the next,
     one far back among hundreds; in a prompt's portion (with and without earlier tokens) and for single tokens."""
     loud = [(0, 299, 0), (0, 298, 63), (0, 297, 64), (0, 296, 127), (0, 295, 128), (0, 290, 5), (1, 200, 200), (1, 199, 191),
@@ -151,19 +152,36 @@ def test_attention_finds_far_keys_and_keys_at_page_borders(dtype):
     # the prompt of sequence 2 and 4 is far behind their one token; sequence 0 continues a portion
     loud = [(s, q, k) for s, q, k in loud if q >= pasts[s] and q < pasts[s] + counts[s]]
     assert len(loud) >= 9
-    got, want = run_latent_attention(4, 16, 8, 12, 24, pasts, counts, dtype, seed=9, loud=loud)
+    got, want = run_latent_attention(4, 16, P, 12, R, pasts, counts, dtype, seed=9, loud=loud)
     torch.testing.assert_close(got, want, **TOL[dtype])
     assert float(want.abs().max()) > 0.5         # the loud keys carry the result
 
 
+@pytest.mark.parametrize("R, P", [(40, 8), (48, 16), (288, 32)])
 @pytest.mark.parametrize("dtype", ["fp32", "bf16"])
 @pytest.mark.parametrize("splits", [2, 5, 16])
-def test_attention_in_slices_is_the_same_attention(splits, dtype):
+def test_attention_in_slices_is_the_same_attention(splits, dtype, R, P):
     pasts, counts = [1000, 70, 0, 511], [1, 1, 1, 1]
-    one = run_latent_attention(6, 16, 8, 16, 40, pasts, counts, dtype, seed=2, loud=[(0, 1000, 2), (3, 511, 448)])
-    cut = run_latent_attention(6, 16, 8, 16, 40, pasts, counts, dtype, seed=2, loud=[(0, 1000, 2), (3, 511, 448)], splits=splits)
+    one = run_latent_attention(6, 16, P, 16, R, pasts, counts, dtype, seed=2, loud=[(0, 1000, 2), (3, 511, 448)])
+    cut = run_latent_attention(6, 16, P, 16, R, pasts, counts, dtype, seed=2, loud=[(0, 1000, 2), (3, 511, 448)], splits=splits)
     torch.testing.assert_close(cut[0], one[1], **TOL[dtype])
     torch.testing.assert_close(cut[0], one[0], rtol=1e-5, atol=1e-5) if dtype == "fp32" else None
+
+
+def test_the_two_bfloat16_attention_kernels_agree():
+    """The tensor-core kernel and the general one on the same bfloat16 inputs: portions behind earlier tokens, single
+    tokens and whole prompts in one step, more heads than a block takes."""
+    args = dict(H=70, dn=8, P=16, dv=8, R=48, pasts=[100, 0, 300, 64], counts=[30, 129, 1, 2], dtype="bf16", seed=4,
+                loud=[(0, 120, 3), (1, 128, 64), (2, 300, 63)])
+    fast, want = run_latent_attention(**args)
+    ops().latent_attention_general_only(True)
+    try:
+        slow, _ = run_latent_attention(**args)
+    finally:
+        ops().latent_attention_general_only(False)
+    torch.testing.assert_close(fast, want, **TOL["bf16"])
+    torch.testing.assert_close(fast, slow, rtol=1e-2, atol=1e-2)
+    assert not torch.equal(fast, slow)          # two kernels did run
 
 
 @pytest.mark.parametrize("dtype", ["fp32", "bf16"])
