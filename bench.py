@@ -588,6 +588,7 @@ def design_point(config: dict, prompt_len: int, batches, steps: int, warmup: int
         out[f"decode_b{batch}_tok_s"] = round(batch / ms * 1e3)
     # where the time goes, launcher by launcher (graphs off so that every launch is seen; cuBLAS products are not)
     eng.stepper.use_graphs = False
+    eng.stepper._graphs.clear()
     lib = ops.lib()
     for label, count in (("prompt", prompt_len), ("token", 1)):
         slots = eng.open(8 if count == 1 else 1)

@@ -18,7 +18,8 @@
 
 namespace slb {
 
-constexpr int kLatRows = 32;      // (token, head) rows of a block
+constexpr int kLatRows = 32;      // (token, head) rows of a block of the general kernel
+constexpr size_t kLatMaxSmem = 227 * 1024;      // dynamic shared memory a block may ask for
 constexpr int kLatWarps = 8;
 constexpr int kLatRowsPerWarp = kLatRows / kLatWarps;
 
@@ -284,7 +285,7 @@ __global__ void __launch_bounds__(kLatWarps * 32) latent_attn_kernel(const Laten
 // from the same shared rows through transposing loads. A block takes at most NTM * 16 value columns (its sums live in
 // registers); a wider latent is shared by several blocks (grid z), each of which forms the scores again.
 template <int NTM>
-__global__ void __launch_bounds__(128) latent_attn_mma_kernel(const LatentAttnArgs a, int nt16, int groups) {
+__global__ void __launch_bounds__(128) latent_attn_mma_kernel(const LatentAttnArgs a, int nt16, int groups, int buffers) {
   pdl_enter();
   extern __shared__ __align__(16) unsigned char lat_raw[];
   const int W = a.R + a.P, ks = a.kstride;
@@ -350,26 +351,45 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(const LatentAttnAr
 #pragma unroll
   for (int i = 0; i < 2 * NTM; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   float m_r[2] = {-INFINITY, -INFINITY}, l_r[2] = {0.f, 0.f};
-  const uint32_t q_base = smem_u32(Qs), k_base = smem_u32(Ks);
+  const uint32_t q_base = smem_u32(Qs);
   const int pieces = W / 8;
 
-  for (int c = c_lo; c < c_hi; ++c) {
+  // a chunk of 64 cache rows into buffer `buf`: rows past the sequence become zeros, never stale values
+  auto load_chunk = [&](int c, int buf) {
     const int k0 = key_lo + c * 64;
     const int nk = min(64, last_pos - k0 + 1);
-    __syncthreads();
-    {
-      const __nv_bfloat16* src = pool + (size_t)trow[k0 / kPageTokens] * kPageTokens * W;
-      for (int i = tid; i < 64 * pieces; i += 128) {
-        const int j = i / pieces, p8 = (i - j * pieces) * 8;
-        __nv_bfloat16* dst = Ks + (size_t)j * ks + p8;
-        if (j < nk) cp_async16(smem_u32(dst), src + (size_t)j * W + p8);
-        else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);      // rows past the sequence: zeros, never stale values
+    const __nv_bfloat16* src = pool + (size_t)trow[k0 / kPageTokens] * kPageTokens * W;
+    __nv_bfloat16* base = Ks + (size_t)buf * 64 * ks;
+    for (int i = tid; i < 64 * pieces; i += 128) {
+      const int j = i / pieces, p8 = (i - j * pieces) * 8;
+      __nv_bfloat16* dst = base + (size_t)j * ks + p8;
+      if (j < nk) cp_async16(smem_u32(dst), src + (size_t)j * W + p8);
+      else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+    }
+    cp_async_commit();
+  };
+  // with two buffers the next chunk is on its way while this one is multiplied
+  __syncthreads();
+  if (buffers == 2 && c_lo < c_hi) load_chunk(c_lo, 0);
+  for (int c = c_lo; c < c_hi; ++c) {
+    const int k0 = key_lo + c * 64;
+    int buf = 0;
+    if (buffers == 2) {
+      buf = (c - c_lo) & 1;
+      if (c + 1 < c_hi) {
+        load_chunk(c + 1, buf ^ 1);
+        cp_async_wait<1>();
+      } else {
+        cp_async_wait<0>();
       }
-      cp_async_commit();
+    } else {
+      __syncthreads();
+      load_chunk(c, 0);
       cp_async_wait<0>();
     }
     __syncthreads();
-    if (!warp_active) continue;
+    const uint32_t k_base = smem_u32(Ks + (size_t)buf * 64 * ks);
+    if (warp_active) {
     float s[8][4];
 #pragma unroll
     for (int j = 0; j < 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
@@ -437,6 +457,8 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(const LatentAttnAr
         }
       }
     }
+    }
+    if (buffers == 2) __syncthreads();      // this buffer is the target of the next iteration's prefetch
   }
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
@@ -589,7 +611,7 @@ extern "C" int slb_latent_attention(const void* q_lat, const void* q_raw, const 
   a.R = R; a.P = P; a.dn = dn; a.rot = rot; a.window = window; a.splits = splits; a.scale = scale;
   cudaStream_t s = (cudaStream_t)stream;
   const bool aligned = ((uintptr_t)q_lat | (uintptr_t)q_raw | (uintptr_t)pool | (uintptr_t)out) % 16 == 0;
-  if (dtype == kBF16 && R % 16 == 0 && (R + P) % 16 == 0 && aligned && (size_t)128 * (R + P + 8) * 2 <= 200 * 1024 &&
+  if (dtype == kBF16 && R % 16 == 0 && (R + P) % 16 == 0 && aligned && (size_t)128 * (R + P + 8) * 2 <= kLatMaxSmem &&
       !slb_latent_force_generic) {
     const int tiles16 = R / 16;
     const int groups = (tiles16 + 15) / 16;
@@ -599,16 +621,17 @@ extern "C" int slb_latent_attention(const void* q_lat, const void* q_raw, const 
     a.hb = H < 64 ? H : 64;
     a.tq = 64 / a.hb;
     const int head_chunks = (H + a.hb - 1) / a.hb;
-    const size_t smem = (size_t)128 * a.kstride * 2;
+    const int buffers = (size_t)192 * a.kstride * 2 <= kLatMaxSmem ? 2 : 1;
+    const size_t smem = (size_t)(64 + 64 * buffers) * a.kstride * 2;
     const dim3 grid((max_count + a.tq - 1) / a.tq, n_seqs, head_chunks * groups * splits), block(128);
 #define SLB_LATM(V)                                                                                              \
   do {                                                                                                           \
     static bool raised = false;                                                                                  \
     if (!raised) {                                                                                               \
-      cudaFuncSetAttribute(latent_attn_mma_kernel<V>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);  \
+      cudaFuncSetAttribute(latent_attn_mma_kernel<V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kLatMaxSmem);   \
       raised = true;                                                                                             \
     }                                                                                                            \
-    launch(latent_attn_mma_kernel<V>, grid, block, smem, s, a, nt16, groups);                                    \
+    launch(latent_attn_mma_kernel<V>, grid, block, smem, s, a, nt16, groups, buffers);                                   \
   } while (0)
     if (nt16 <= 4) SLB_LATM(4); else if (nt16 <= 8) SLB_LATM(8); else SLB_LATM(16);
 #undef SLB_LATM

@@ -6,8 +6,9 @@
 // routed experts can therefore be recorded once and replayed.
 //
 //   moe_route_kernel     logits = W_r h + b in float32, the `top` largest (lowest index first among equals), weights
-//                        = softmax over the chosen logits; counts the pairs of each expert
-//   moe_group_kernel     place[pair] = where the pair's row lies in the expert-ordered list, list[place] = pair
+//                        = softmax over the chosen logits
+//   moe_group_kernel     counts the pairs of each expert; place[pair] = where the pair's row lies in the
+//                        expert-ordered list, list[place] = pair
 //   moe_gate_up_kernel   act[place, j] = f(gate_e[j] . h) * (up_e[j] . h), f = silu or relu
 //   moe_down_kernel      y[pair, :] = weight[pair] * (down_e act[place])   (float32)
 //   moe_combine_kernel   x[t, :] += sum over the token's choices of y, in the order of the choices
@@ -20,12 +21,56 @@ namespace slb {
 constexpr int kMoeTile = 32;        // rows (pairs) of a product tile
 constexpr int kMoeCols = 64;        // output columns of a product tile
 constexpr int kMoeK = 32;           // inner-dimension slice staged in shared memory
+constexpr int kMoeFewPairs = 64;    // up to this many (token, choice) pairs a step runs a warp per output instead of tiles
+
+// Router logits for many tokens: z[t, e] = w[e] . h[t] + b[e], float32, k ascending. A block takes 32 tokens and 16
+// experts; the tokens' rows and the experts' rows go through shared memory 128 values at a time; a lane is a token,
+// a warp takes two of the experts.
+template <typename T>
+__global__ void __launch_bounds__(256) moe_logits_kernel(const T* __restrict__ h, const float* __restrict__ wr,
+                                                         const float* __restrict__ bias, float* __restrict__ z, int tokens,
+                                                         int dim, int E) {
+  pdl_enter();
+  constexpr int KC = 128;
+  __shared__ float hs[32 * (KC + 1)];
+  __shared__ float ws[16 * KC];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t0 = blockIdx.x * 32, e0 = blockIdx.y * 16;
+  float acc0 = 0.f, acc1 = 0.f;
+  for (int k0 = 0; k0 < dim; k0 += KC) {
+    const int nk = min(KC, dim - k0);
+    __syncthreads();
+    for (int i = threadIdx.x; i < 32 * KC; i += 256) {
+      const int r = i / KC, k = i % KC;
+      hs[r * (KC + 1) + k] = (t0 + r < tokens && k < nk) ? to_f32(h[(size_t)(t0 + r) * dim + k0 + k]) : 0.f;
+    }
+    for (int i = threadIdx.x; i < 16 * KC; i += 256) {
+      const int r = i / KC, k = i % KC;
+      ws[i] = (e0 + r < E && k < nk) ? wr[(size_t)(e0 + r) * dim + k0 + k] : 0.f;
+    }
+    __syncthreads();
+    const float* mine = hs + lane * (KC + 1);
+    const float* wa = ws + warp * KC;
+    const float* wb = ws + (warp + 8) * KC;
+#pragma unroll 8
+    for (int k = 0; k < KC; ++k) {
+      const float x = mine[k];
+      acc0 = fmaf(x, wa[k], acc0);
+      acc1 = fmaf(x, wb[k], acc1);
+    }
+  }
+  if (t0 + lane < tokens) {
+    const int ea = e0 + warp, eb = e0 + warp + 8;
+    if (ea < E) z[(size_t)(t0 + lane) * E + ea] = acc0 + (bias ? bias[ea] : 0.f);
+    if (eb < E) z[(size_t)(t0 + lane) * E + eb] = acc1 + (bias ? bias[eb] : 0.f);
+  }
+}
 
 // One warp per token.
 template <typename T>
 __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restrict__ wr, const float* __restrict__ bias,
-                                 int* __restrict__ choice, float* __restrict__ weight, int* __restrict__ rank,
-                                 int* __restrict__ counts, int tokens, int dim, int E, int top) {
+                                 const float* __restrict__ given, int* __restrict__ choice, float* __restrict__ weight,
+                                 int tokens, int dim, int E, int top) {
   pdl_enter();
   extern __shared__ float sm[];
   const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -33,6 +78,9 @@ __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restric
   if (t >= tokens) return;
   float* z = sm + (size_t)warp * E;
   const T* row = h + (size_t)t * dim;
+  if (given != nullptr) {            // the logits were formed by moe_logits_kernel
+    for (int e = lane; e < E; e += 32) z[e] = given[(size_t)t * E + e];
+  } else
   for (int e = 0; e < E; ++e) {
     const float* w = wr + (size_t)e * dim;
     float s = 0.f;
@@ -66,28 +114,41 @@ __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restric
     }
     __syncwarp();
   }
-  for (int k = lane; k < top; k += 32) {
-    weight[(size_t)t * top + k] /= mass;
-    rank[(size_t)t * top + k] = atomicAdd(&counts[choice[(size_t)t * top + k]], 1);
-  }
+  for (int k = lane; k < top; k += 32) weight[(size_t)t * top + k] /= mass;
 }
 
-// place[pair] = first row of the pair's expert + the pair's rank there; list[place] = pair.
-__global__ void moe_group_kernel(const int* __restrict__ choice, const int* __restrict__ rank,
-                                 const int* __restrict__ counts, int* __restrict__ place, int* __restrict__ list,
-                                 int pairs, int E) {
+// One block lays the pairs out expert by expert: counts[e], then place[pair] = first row of the pair's expert + the
+// pair's turn there, and list[place] = pair. The turns come from shared-memory counters, so which of an expert's rows
+// a pair gets may differ from run to run; every pair's result is computed from its own row alone, so nothing else does.
+__global__ void __launch_bounds__(1024) moe_group_kernel(const int* __restrict__ choice, int* __restrict__ counts,
+                                                         int* __restrict__ place, int* __restrict__ list, int pairs, int E) {
   pdl_enter();
-  extern __shared__ int first[];
-  if (threadIdx.x == 0) {
+  extern __shared__ int sh[];          // [E] counts, then [E] first rows / cursors
+  int* cnt = sh;
+  int* cur = sh + E;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
+  __syncthreads();
+  for (int p = threadIdx.x; p < pairs; p += blockDim.x) atomicAdd(&cnt[choice[p]], 1);
+  __syncthreads();
+  if (threadIdx.x < 32) {              // exclusive scan over the experts, 32 at a time
     int run = 0;
-    for (int e = 0; e < E; ++e) {
-      first[e] = run;
-      run += counts[e];
+    for (int e0 = 0; e0 < E; e0 += 32) {
+      const int e = e0 + threadIdx.x;
+      const int c = e < E ? cnt[e] : 0;
+      int inc = c;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, inc, o);
+        if ((int)threadIdx.x >= o) inc += v;
+      }
+      if (e < E) cur[e] = run + inc - c;
+      run += __shfl_sync(0xffffffffu, inc, 31);
     }
   }
   __syncthreads();
-  for (int p = blockIdx.x * blockDim.x + threadIdx.x; p < pairs; p += gridDim.x * blockDim.x) {
-    const int at = first[choice[p]] + rank[p];
+  for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = cnt[e];
+  for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+    const int at = atomicAdd(&cur[choice[p]], 1);
     place[p] = at;
     list[at] = p;
   }
@@ -329,6 +390,88 @@ __global__ void __launch_bounds__(128) moe_mma_kernel(const __nv_bfloat16* __res
   }
 }
 
+// ---- few pairs (single-token steps): a warp per output, every weight row streamed once per pair that uses it ----
+// grid (pairs, column groups of 8): act[place[pair], j] = f(gate_e[j] . h[token]) * (up_e[j] . h[token]).
+template <typename T>
+__global__ void __launch_bounds__(256) moe_few_gate_up_kernel(const T* __restrict__ h, const T* __restrict__ w_gu,
+                                                              const int* __restrict__ choice, const int* __restrict__ place,
+                                                              T* __restrict__ act, int top, int dim, int ff, int relu) {
+  pdl_enter();
+  const int pair = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int j = blockIdx.y * 8 + warp;
+  if (j >= ff) return;
+  const int e = choice[pair];
+  const T* x = h + (size_t)(pair / top) * dim;
+  const T* wg = w_gu + ((size_t)e * 2 * ff + j) * dim;
+  const T* wu = wg + (size_t)ff * dim;
+  float g = 0.f, u = 0.f;
+  if constexpr (sizeof(T) == 2) {
+    if (dim % 8 == 0) {
+      for (int k = lane * 8; k < dim; k += 256) {
+        float xf[8], gf[8], uf[8];
+        unpack8(*reinterpret_cast<const Bf16x8*>(x + k), xf);
+        unpack8(*reinterpret_cast<const Bf16x8*>(wg + k), gf);
+        unpack8(*reinterpret_cast<const Bf16x8*>(wu + k), uf);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          g = fmaf(xf[i], gf[i], g);
+          u = fmaf(xf[i], uf[i], u);
+        }
+      }
+    } else {
+      for (int k = lane; k < dim; k += 32) {
+        const float xv = to_f32(x[k]);
+        g = fmaf(xv, to_f32(wg[k]), g);
+        u = fmaf(xv, to_f32(wu[k]), u);
+      }
+    }
+  } else {
+    for (int k = lane; k < dim; k += 32) {
+      const float xv = to_f32(x[k]);
+      g = fmaf(xv, to_f32(wg[k]), g);
+      u = fmaf(xv, to_f32(wu[k]), u);
+    }
+  }
+  g = warp_sum(g);
+  u = warp_sum(u);
+  if (lane == 0) {
+    const float f = relu ? fmaxf(g, 0.f) : g / (1.0f + expf(-g));
+    act[(size_t)place[pair] * ff + j] = from_f32<T>(f * u);
+  }
+}
+
+// grid (pairs, column groups of 8): y[pair, n] = weight[pair] * (down_e[n] . act[place[pair]]).
+template <typename T>
+__global__ void __launch_bounds__(256) moe_few_down_kernel(const T* __restrict__ act, const T* __restrict__ w_down,
+                                                           const int* __restrict__ choice, const int* __restrict__ place,
+                                                           const float* __restrict__ weight, float* __restrict__ y, int dim,
+                                                           int ff) {
+  pdl_enter();
+  const int pair = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = blockIdx.y * 8 + warp;
+  if (n >= dim) return;
+  const T* a = act + (size_t)place[pair] * ff;
+  const T* w = w_down + ((size_t)choice[pair] * dim + n) * ff;
+  float s = 0.f;
+  if constexpr (sizeof(T) == 2) {
+    if (ff % 8 == 0) {
+      for (int k = lane * 8; k < ff; k += 256) {
+        float af[8], wf[8];
+        unpack8(*reinterpret_cast<const Bf16x8*>(a + k), af);
+        unpack8(*reinterpret_cast<const Bf16x8*>(w + k), wf);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s = fmaf(af[i], wf[i], s);
+      }
+    } else {
+      for (int k = lane; k < ff; k += 32) s = fmaf(to_f32(a[k]), to_f32(w[k]), s);
+    }
+  } else {
+    for (int k = lane; k < ff; k += 32) s = fmaf(to_f32(a[k]), to_f32(w[k]), s);
+  }
+  s = warp_sum(s);
+  if (lane == 0) y[(size_t)pair * dim + n] = weight[pair] * s;
+}
+
 __global__ void moe_combine_kernel(float* __restrict__ x, const float* __restrict__ y, int top, int dim, size_t total) {
   pdl_enter();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -345,40 +488,49 @@ __global__ void moe_combine_kernel(float* __restrict__ x, const float* __restric
 
 using namespace slb;
 
-// choice, rank, place, list: int32 [tokens * top]; weight: float32 [tokens * top]; counts: int32 [E] (zeroed here).
+// choice, place, list: int32 [tokens * top]; weight: float32 [tokens * top]; counts: int32 [E] (written here).
+// logits: float32 scratch [tokens, E], or null (then every token's warp forms its own logits).
 extern "C" int slb_moe_route(const void* h, const float* w_router, const float* bias, int* choice, float* weight,
-                             int* rank, int* counts, int* place, int* list, int tokens, int dim, int E, int top,
-                             int dtype, void* stream) {
+                             int* rank, int* counts, int* place, int* list, float* logits, int tokens, int dim, int E,
+                             int top, int dtype, void* stream) {
   SLB_REQUIRE(tokens >= 0 && dim > 0 && E > 0 && top > 0 && top <= E, "moe_route: tokens=%d dim=%d experts=%d top=%d",
               tokens, dim, E, top);
   SLB_REQUIRE(E <= 4096, "moe_route: at most 4096 experts, got %d", E);
   SLB_REQUIRE(dtype == kF32 || dtype == kBF16, "moe_route: unknown dtype %d", dtype);
   if (tokens == 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
-  cudaError_t e = cudaMemsetAsync(counts, 0, sizeof(int) * E, s);
-  SLB_REQUIRE(e == cudaSuccess, "moe_route: clearing the counts failed (%s)", cudaGetErrorString(e));
+  (void)rank;      // kept in the signature: callers hand over a table that older versions filled
   const int warps = E <= 1024 ? 4 : 1;
   const size_t smem = (size_t)warps * E * sizeof(float);
   const dim3 grid((tokens + warps - 1) / warps), block(warps * 32);
+  // from a few tokens on the logits are formed 32 tokens and 16 experts at a time, each weight read once a block
+  const float* given = nullptr;
+  if (logits != nullptr && tokens >= 16) {
+    const dim3 lg((tokens + 31) / 32, (E + 15) / 16), lb(256);
+    if (dtype == kF32) launch(moe_logits_kernel<float>, lg, lb, 0, s, (const float*)h, w_router, bias, logits, tokens, dim, E);
+    else launch(moe_logits_kernel<__nv_bfloat16>, lg, lb, 0, s, (const __nv_bfloat16*)h, w_router, bias, logits, tokens, dim, E);
+    int rc0 = check_launch("moe_logits");
+    if (rc0) return rc0;
+    given = logits;
+  }
   if (dtype == kF32)
-    launch(moe_route_kernel<float>, grid, block, smem, s, (const float*)h, w_router, bias, choice, weight, rank, counts, tokens, dim, E, top);
+    launch(moe_route_kernel<float>, grid, block, smem, s, (const float*)h, w_router, bias, given, choice, weight, tokens, dim, E, top);
   else
-    launch(moe_route_kernel<__nv_bfloat16>, grid, block, smem, s, (const __nv_bfloat16*)h, w_router, bias, choice, weight, rank,
-           counts, tokens, dim, E, top);
+    launch(moe_route_kernel<__nv_bfloat16>, grid, block, smem, s, (const __nv_bfloat16*)h, w_router, bias, given, choice, weight,
+           tokens, dim, E, top);
   int rc = check_launch("moe_route");
   if (rc) return rc;
   const int pairs = tokens * top;
-  int blocks = (pairs + 255) / 256;
-  if (blocks > sm_count() * 4) blocks = sm_count() * 4;
-  launch(moe_group_kernel, dim3(blocks), dim3(256), sizeof(int) * E, s, (const int*)choice, (const int*)rank, (const int*)counts, place,
-         list, pairs, E);
+  launch(moe_group_kernel, dim3(1), dim3(pairs >= 1024 ? 1024 : 256), 2 * sizeof(int) * E, s, (const int*)choice, counts, place, list,
+         pairs, E);
   return check_launch("moe_group");
 }
 
 // act: [tokens * top, ff] in the run dtype; y: float32 [tokens * top, dim]; x: the float32 stream [tokens, dim].
+// choice and place (from slb_moe_route) serve steps of few pairs, which run a warp per output instead of tiles.
 extern "C" int slb_moe_experts(const void* h, const void* w_gu, const void* w_down, const int* counts, const int* list,
-                               const float* weight, void* act, float* y, float* x, int tokens, int dim, int ff, int E,
-                               int top, int relu, int dtype, void* stream) {
+                               const int* choice, const int* place, const float* weight, void* act, float* y, float* x,
+                               int tokens, int dim, int ff, int E, int top, int relu, int dtype, void* stream) {
   SLB_REQUIRE(tokens >= 0 && dim > 0 && ff > 0 && E > 0 && top > 0, "moe_experts: tokens=%d dim=%d ff=%d experts=%d top=%d",
               tokens, dim, ff, E, top);
   SLB_REQUIRE(dtype == kF32 || dtype == kBF16, "moe_experts: unknown dtype %d", dtype);
@@ -391,7 +543,18 @@ extern "C" int slb_moe_experts(const void* h, const void* w_gu, const void* w_do
   const dim3 block(256);
   const dim3 g1((unsigned)tiles, (ff + 31) / 32), g2((unsigned)tiles, (dim + kMoeCols - 1) / kMoeCols);
   const bool aligned = ((uintptr_t)h | (uintptr_t)w_gu | (uintptr_t)w_down | (uintptr_t)act) % 16 == 0;
-  if (dtype == kBF16 && dim % 8 == 0 && ff % 8 == 0 && aligned) {
+  if (pairs <= kMoeFewPairs && choice != nullptr && place != nullptr && (dtype == kF32 || aligned)) {
+    const dim3 f1((unsigned)pairs, (ff + 7) / 8), f2((unsigned)pairs, (dim + 7) / 8);
+    if (dtype == kF32) {
+      launch(moe_few_gate_up_kernel<float>, f1, block, 0, s, (const float*)h, (const float*)w_gu, choice, place, (float*)act, top, dim, ff, relu);
+      launch(moe_few_down_kernel<float>, f2, block, 0, s, (const float*)act, (const float*)w_down, choice, place, weight, y, dim, ff);
+    } else {
+      launch(moe_few_gate_up_kernel<__nv_bfloat16>, f1, block, 0, s, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w_gu, choice, place,
+             (__nv_bfloat16*)act, top, dim, ff, relu);
+      launch(moe_few_down_kernel<__nv_bfloat16>, f2, block, 0, s, (const __nv_bfloat16*)act, (const __nv_bfloat16*)w_down, choice, place,
+             weight, y, dim, ff);
+    }
+  } else if (dtype == kBF16 && dim % 8 == 0 && ff % 8 == 0 && aligned) {
     const long long tiles64 = pairs / kMmaRows + (pairs < E ? pairs : E);
     launch(moe_mma_kernel<true>, dim3((unsigned)tiles64, (ff + 63) / 64), dim3(128), 0, s, (const __nv_bfloat16*)h,
            (const __nv_bfloat16*)w_gu, counts, list, weight, (__nv_bfloat16*)act, (float*)nullptr, E, top, dim, ff, relu);

@@ -700,13 +700,13 @@ def latent_attention_general_only(on: bool) -> None:
 
 def latent_splits(n_seqs: int, heads: int, max_count: int, max_len: int, sms: int | None = None) -> int:
     """Into how many slices the keys of a step are cut: none while the step's own blocks fill the SMs, else as many
-    as it takes to give every SM about two blocks, each slice at least four pages long."""
+    as it takes to give every SM about two blocks, each slice at least two pages long."""
     sms = sms or sm_count()
-    hb = min(heads, 32)
-    blocks = n_seqs * -(-max_count // (32 // hb)) * -(-heads // hb)
-    if blocks >= sms or max_len <= 256:
+    hb = min(heads, 64)
+    blocks = n_seqs * -(-max_count // (64 // hb)) * -(-heads // hb)
+    if blocks >= sms or max_len <= 128:
         return 1
-    return int(max(1, min(2 * sms // max(blocks, 1), max_len // 256, 64)))
+    return int(max(1, min(2 * sms // max(blocks, 1), max_len // 128, 64)))
 
 
 def latent_scratch_floats(tokens: int, heads: int, rank: int, splits: int) -> int:
@@ -748,11 +748,12 @@ def latent_gate(val, g, y, stream=None) -> None:
 
 
 # ---- routed experts (csrc/moe.cu) ----
-def moe_route(h, w_router, bias, choice, weight, rank, counts, place, order, top: int, stream=None) -> None:
+def moe_route(h, w_router, bias, choice, weight, rank, counts, place, order, top: int, stream=None, logits=None) -> None:
     """Router logits in float32, the ``top`` largest per token, softmax over those; then the (token, choice) pairs are
     laid out expert by expert: counts [experts], place [T * top] (a pair's row in that order), order [T * top] (the
-    pair at each row). choice, rank int32 [T * top]; weight float32 [T * top]."""
-    _cuda(h, w_router, bias, choice, weight, rank, counts, place, order)
+    pair at each row). choice, rank int32 [T * top]; weight float32 [T * top]. ``logits``: float32 scratch
+    [T, experts]; with it, steps of many tokens form their logits 32 tokens at a time (the same sums, k ascending)."""
+    _cuda(h, w_router, bias, choice, weight, rank, counts, place, order, logits)
     T, d = h.shape
     E = w_router.shape[0]
     _need(h.dtype in DT and w_router.dtype == torch.float32 and w_router.shape == (E, d), "moe_route: input or router matrix")
@@ -761,15 +762,19 @@ def moe_route(h, w_router, bias, choice, weight, rank, counts, place, order, top
         _need(t.dtype == torch.int32 and t.numel() >= T * top, "moe_route: int32 tables of tokens * top entries")
     _need(weight.dtype == torch.float32 and weight.numel() >= T * top and counts.dtype == torch.int32 and counts.numel() >= E,
           "moe_route: weights or counts")
+    _need(logits is None or (logits.dtype == torch.float32 and logits.numel() >= T * E), "moe_route: scratch for the logits")
     lib().call("slb_moe_route", _p(h), _p(w_router), _p(bias), _p(choice), _p(weight), _p(rank), _p(counts), _p(place),
-               _p(order), T, d, E, int(top), DT[h.dtype], stream if stream is not None else current_stream())
+               _p(order), _p(logits), T, d, E, int(top), DT[h.dtype], stream if stream is not None else current_stream())
 
 
 def moe_experts(h, w_gate_up, w_down, counts, order, weight, act, y, x, top: int, activation: str = "silu",
-                stream=None) -> None:
+                stream=None, choice=None, place=None) -> None:
     """x[t] += sum over the token's choices of weight * down_e(f(gate_e h) * (up_e h)). w_gate_up [experts, 2 * ff, d]
-    (gate rows, then up rows), w_down [experts, d, ff]; act [T * top, ff] and y [T * top, d] float32 are scratch."""
-    _cuda(h, w_gate_up, w_down, counts, order, weight, act, y, x)
+    (gate rows, then up rows), w_down [experts, d, ff]; act [T * top, ff] and y [T * top, d] float32 are scratch.
+    With ``choice`` and ``place`` (from ``moe_route``) a step of few pairs runs a warp per output instead of tiles."""
+    _cuda(h, w_gate_up, w_down, counts, order, weight, act, y, x, choice, place)
+    for t in (choice, place):
+        _need(t is None or (t.dtype == torch.int32 and t.numel() >= h.shape[0] * top), "moe_experts: choice and place tables")
     T, d = h.shape
     E, ff2, _ = w_gate_up.shape
     ff = ff2 // 2
@@ -778,6 +783,6 @@ def moe_experts(h, w_gate_up, w_down, counts, order, weight, act, y, x, top: int
     _need(act.shape == (T * top, ff) and y.shape == (T * top, d) and y.dtype == torch.float32, "moe_experts: scratch")
     _need(x.shape == (T, d) and x.dtype == torch.float32, "moe_experts: the stream")
     _need(activation in ACTIVATIONS, f"moe_experts: activation {activation!r}")
-    lib().call("slb_moe_experts", _p(h), _p(w_gate_up), _p(w_down), _p(counts), _p(order), _p(weight), _p(act), _p(y),
+    lib().call("slb_moe_experts", _p(h), _p(w_gate_up), _p(w_down), _p(counts), _p(order), _p(choice), _p(place), _p(weight), _p(act), _p(y),
                _p(x), T, d, ff, E, int(top), ACTIVATIONS[activation], DT[h.dtype],
                stream if stream is not None else current_stream())

@@ -5,7 +5,7 @@ dtype). A token uses the ``top`` experts with the largest logits, weighted by th
 and an expert is down(act(gate h) * (up h)). The part's output, the weighted sum, is added into the stream.
 
 The experts' matrices are stacked at load time ([experts, 2 * ff, hidden] for gate and up, [experts, hidden, ff]
-for down). A step runs five kernels (``csrc/moe.cu``): router and counts, the expert-ordered list of (token,
+for down). A step runs five kernels (``csrc/moe.cu``): router, the counts and the expert-ordered list of (token,
 choice) pairs, gate/up with the activation, down scaled by the pair's weight, and the sum over a token's choices
 in the order of the choices. None of them needs the host to know the counts, so the part can be recorded in a
 CUDA graph like any other.
@@ -60,8 +60,10 @@ class RoutedExperts(Part):
         weight = ws.take((pairs,), torch.float32)
         act = ws.take((pairs, s.intermediate), dt)
         y = ws.take((pairs, s.hidden), torch.float32)
-        ops.moe_route(h, self.w_router, self.bias, choice, weight, rank, counts, place, order, s.top, b.stream)
-        ops.moe_experts(h, self.w_gate_up, self.w_down, counts, order, weight, act, y, x, s.top, s.activation, b.stream)
+        logits = ws.take((T, s.experts), torch.float32)
+        ops.moe_route(h, self.w_router, self.bias, choice, weight, rank, counts, place, order, s.top, b.stream, logits)
+        ops.moe_experts(h, self.w_gate_up, self.w_down, counts, order, weight, act, y, x, s.top, s.activation, b.stream,
+                        choice, place)
         ws.release(mark)
 
 

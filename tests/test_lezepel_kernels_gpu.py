@@ -216,11 +216,13 @@ def test_router_and_experts(T, d, ff, E, top, dtype):
     choice, rank, place, order = (torch.empty(pairs, dtype=torch.int32, device=DEV) for _ in range(4))
     counts = torch.empty(E, dtype=torch.int32, device=DEV)
     weight = torch.empty(pairs, dtype=torch.float32, device=DEV)
-    o.moe_route(h.to(DEV), w["router"].to(DEV), w["router.b"].to(DEV), choice, weight, rank, counts, place, order, top)
+    logits = torch.empty(T, E, dtype=torch.float32, device=DEV) if T != 77 else None      # with and without the scratch
+    o.moe_route(h.to(DEV), w["router"].to(DEV), w["router.b"].to(DEV), choice, weight, rank, counts, place, order, top,
+                logits=logits)
     z = h.double() @ w["router"].double().T + w["router.b"].double()
     val, idx = torch.topk(z, top, dim=-1)
     assert torch.equal(choice.cpu().view(T, top).long(), idx)
-    torch.testing.assert_close(weight.cpu().view(T, top).double(), torch.softmax(val, -1), rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(weight.cpu().view(T, top).double(), torch.softmax(val, -1), rtol=1e-4, atol=2e-5)
     assert torch.equal(counts.cpu().long(), torch.bincount(idx.reshape(-1), minlength=E))
     # the expert-ordered list holds every pair once, grouped by expert
     lst = order.cpu().long()
@@ -232,7 +234,10 @@ def test_router_and_experts(T, d, ff, E, top, dtype):
     act = torch.empty(pairs, ff, dtype=dt, device=DEV)
     y = torch.empty(pairs, d, dtype=torch.float32, device=DEV)
     x = x0.clone().to(DEV)
-    o.moe_experts(h.to(DEV), gu, dn, counts, order, weight, act, y, x, top, "silu")
+    o.moe_experts(h.to(DEV), gu, dn, counts, order, weight, act, y, x, top, "silu", choice=choice, place=place)
+    x2 = x0.clone().to(DEV)          # and through the tiles whatever the number of pairs
+    o.moe_experts(h.to(DEV), gu, dn, counts, order, weight, act, y, x2, top, "silu")
+    torch.testing.assert_close(x2, x, **TOL[dtype])
     want = x0.double() + plain.routed_experts(h.double(), {k: v.double() for k, v in w.items()}, "", {"router": {"experts": E, "top": top}})
     torch.testing.assert_close(x.cpu().double(), want, **TOL[dtype])
 
