@@ -307,16 +307,17 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(const LatentAttnAr
   const __nv_bfloat16* pool = (const __nv_bfloat16*)a.pool;
   const int tok0 = a.seq_start[seq] + t0;
   const int half = a.rot / 2;
+  // queries: a warp takes every fourth row; dead rows become zeros
   for (int r = warp; r < 64; r += 4) {
     const int tq = r / a.hb, hh = r % a.hb;
     __nv_bfloat16* qs = Qs + (size_t)r * ks;
     if (!(tq < nt && hh < nh)) {
-      for (int i = lane; i < W; i += 32) qs[i] = __float2bfloat16_rn(0.f);
+      for (int i = lane * 8; i < W; i += 256) *reinterpret_cast<uint4*>(qs + i) = make_uint4(0, 0, 0, 0);
       continue;
     }
     const int tok = tok0 + tq, h = h0 + hh, pos = past + t0 + tq;
     const __nv_bfloat16* ql = q_lat + ((size_t)h * a.T + tok) * a.R;
-    for (int i = lane; i < a.R; i += 32) qs[i] = ql[i];
+    for (int i = lane * 8; i < a.R; i += 256) *reinterpret_cast<uint4*>(qs + i) = *reinterpret_cast<const uint4*>(ql + i);
     const __nv_bfloat16* qr = q_raw + ((size_t)tok * a.H + h) * (a.dn + a.P) + a.dn;
     for (int i = lane; i < a.P; i += 32) {
       float v = __bfloat162float(qr[i]);
@@ -497,30 +498,45 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(const LatentAttnAr
   }
 }
 
-// One warp per (token, head): joins the slices in slice order.
+// One block per (token, head): the slices' factors exp(m_s - m) / mass are formed once, then every thread joins its
+// columns over the slices in slice order.
 template <typename T>
-__global__ void latent_merge_kernel(const float* __restrict__ parts, T* __restrict__ out, int rows, int Tn, int H, int R,
-                                    int splits) {
+__global__ void __launch_bounds__(128) latent_merge_kernel(const float* __restrict__ parts, T* __restrict__ out, int rows, int Tn,
+                                                           int H, int R, int splits) {
   pdl_enter();
-  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-  if (row >= rows) return;
+  __shared__ float factor[64];
+  const int row = blockIdx.x;
   const int tok = row / H, h = row % H;
-  float mx = -INFINITY;
-  for (int s = 0; s < splits; ++s) mx = fmaxf(mx, parts[((size_t)s * rows + row) * (R + 2) + R]);
-  float mass = 0.f;
-  for (int s = 0; s < splits; ++s) {
-    const float* p = parts + ((size_t)s * rows + row) * (R + 2);
-    if (p[R] != -INFINITY) mass += p[R + 1] * expf(p[R] - mx);
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    float m0 = lane < splits ? parts[((size_t)lane * rows + row) * (R + 2) + R] : -INFINITY;
+    float m1 = lane + 32 < splits ? parts[((size_t)(lane + 32) * rows + row) * (R + 2) + R] : -INFINITY;
+    const float mx = warp_max(fmaxf(m0, m1));
+    float f0 = m0 == -INFINITY ? 0.f : expf(m0 - mx), f1 = m1 == -INFINITY ? 0.f : expf(m1 - mx);
+    float l0 = lane < splits ? parts[((size_t)lane * rows + row) * (R + 2) + R + 1] : 0.f;
+    float l1 = lane + 32 < splits ? parts[((size_t)(lane + 32) * rows + row) * (R + 2) + R + 1] : 0.f;
+    // the mass is summed in slice order by one lane, so that the result does not depend on the lanes' tree
+    factor[lane] = f0 * l0;
+    factor[lane + 32] = f1 * l1;
+    __syncwarp();
+    float mass = 0.f;
+    if (lane == 0)
+      for (int s = 0; s < splits; ++s) mass += factor[s];
+    mass = __shfl_sync(0xffffffffu, mass, 0);
+    const float inv = mass > 0.f ? 1.0f / mass : 0.f;
+    __syncwarp();
+    factor[lane] = f0 * inv;
+    factor[lane + 32] = f1 * inv;
   }
-  const float inv = mass > 0.f ? 1.0f / mass : 0.f;
+  __syncthreads();
   T* o = out + ((size_t)h * Tn + tok) * R;
-  for (int d = lane; d < R; d += 32) {
+  for (int d = threadIdx.x; d < R; d += blockDim.x) {
     float v = 0.f;
     for (int s = 0; s < splits; ++s) {
-      const float* p = parts + ((size_t)s * rows + row) * (R + 2);
-      if (p[R] != -INFINITY) v = fmaf(p[d], expf(p[R] - mx), v);
+      const float f = factor[s];
+      if (f != 0.f) v = fmaf(parts[((size_t)s * rows + row) * (R + 2) + d], f, v);
     }
-    o[d] = from_f32<T>(v * inv);
+    o[d] = from_f32<T>(v);
   }
 }
 
@@ -604,6 +620,7 @@ extern "C" int slb_latent_attention(const void* q_lat, const void* q_raw, const 
               "latent_attention: seqs=%d max=%d heads=%d rank=%d rot_dim=%d splits=%d", n_seqs, max_count, H, R, P, splits);
   SLB_REQUIRE(dtype == kF32 || dtype == kBF16, "latent_attention: unknown dtype %d", dtype);
   SLB_REQUIRE(splits == 1 || parts != nullptr, "latent_attention: slices need scratch memory");
+  SLB_REQUIRE(splits <= 64, "latent_attention: at most 64 slices, got %d", splits);
   if (n_seqs == 0 || max_count == 0 || T == 0) return 0;
   LatentAttnArgs a;
   a.q_lat = q_lat; a.q_raw = q_raw; a.pool = pool; a.out = out; a.parts = parts; a.cos_t = cos_t; a.sin_t = sin_t;
@@ -638,7 +655,7 @@ extern "C" int slb_latent_attention(const void* q_lat, const void* q_raw, const 
     int rc = check_launch("latent_attention");
     if (rc || splits == 1) return rc;
     const int rows = T * H;
-    launch(latent_merge_kernel<__nv_bfloat16>, dim3((rows + 7) / 8), dim3(256), 0, s, (const float*)parts,
+    launch(latent_merge_kernel<__nv_bfloat16>, dim3(rows), dim3(128), 0, s, (const float*)parts,
            (__nv_bfloat16*)out, rows, T, H, R, splits);
     return check_launch("latent_merge");
   }
@@ -674,9 +691,9 @@ extern "C" int slb_latent_attention(const void* q_lat, const void* q_raw, const 
   if (rc || splits == 1) return rc;
   const int rows = T * H;
   if (dtype == kF32)
-    launch(latent_merge_kernel<float>, dim3((rows + 7) / 8), dim3(256), 0, s, (const float*)parts, (float*)out, rows, T, H, R, splits);
+    launch(latent_merge_kernel<float>, dim3(rows), dim3(128), 0, s, (const float*)parts, (float*)out, rows, T, H, R, splits);
   else
-    launch(latent_merge_kernel<__nv_bfloat16>, dim3((rows + 7) / 8), dim3(256), 0, s, (const float*)parts,
+    launch(latent_merge_kernel<__nv_bfloat16>, dim3(rows), dim3(128), 0, s, (const float*)parts,
            (__nv_bfloat16*)out, rows, T, H, R, splits);
   return check_launch("latent_merge");
 }

@@ -40,9 +40,19 @@ __global__ void __launch_bounds__(256) moe_logits_kernel(const T* __restrict__ h
   for (int k0 = 0; k0 < dim; k0 += KC) {
     const int nk = min(KC, dim - k0);
     __syncthreads();
-    for (int i = threadIdx.x; i < 32 * KC; i += 256) {
-      const int r = i / KC, k = i % KC;
-      hs[r * (KC + 1) + k] = (t0 + r < tokens && k < nk) ? to_f32(h[(size_t)(t0 + r) * dim + k0 + k]) : 0.f;
+    if (sizeof(T) == 2 && dim % 8 == 0 && ((uintptr_t)h & 15) == 0) {      // 16 bytes of a row per load
+      for (int i = threadIdx.x; i < 32 * (KC / 8); i += 256) {
+        const int r = i / (KC / 8), k = (i % (KC / 8)) * 8;
+        float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        if (t0 + r < tokens && k < nk) unpack8(*reinterpret_cast<const Bf16x8*>(h + (size_t)(t0 + r) * dim + k0 + k), f);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) hs[r * (KC + 1) + k + u] = f[u];
+      }
+    } else {
+      for (int i = threadIdx.x; i < 32 * KC; i += 256) {
+        const int r = i / KC, k = i % KC;
+        hs[r * (KC + 1) + k] = (t0 + r < tokens && k < nk) ? to_f32(h[(size_t)(t0 + r) * dim + k0 + k]) : 0.f;
+      }
     }
     for (int i = threadIdx.x; i < 16 * KC; i += 256) {
       const int r = i / KC, k = i % KC;
@@ -66,29 +76,38 @@ __global__ void __launch_bounds__(256) moe_logits_kernel(const T* __restrict__ h
   }
 }
 
-// One warp per token.
+// One block of eight warps per token. Without given logits a warp forms the logits of every eighth expert (the lanes
+// share the row, four partial sums each, joined in a fixed order); warp 0 then picks the `top` largest.
 template <typename T>
-__global__ void moe_route_kernel(const T* __restrict__ h, const float* __restrict__ wr, const float* __restrict__ bias,
-                                 const float* __restrict__ given, int* __restrict__ choice, float* __restrict__ weight,
-                                 int tokens, int dim, int E, int top) {
+__global__ void __launch_bounds__(256) moe_route_kernel(const T* __restrict__ h, const float* __restrict__ wr,
+                                                        const float* __restrict__ bias, const float* __restrict__ given,
+                                                        int* __restrict__ choice, float* __restrict__ weight, int tokens,
+                                                        int dim, int E, int top) {
   pdl_enter();
-  extern __shared__ float sm[];
-  const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * warps + warp;
-  if (t >= tokens) return;
-  float* z = sm + (size_t)warp * E;
+  extern __shared__ float z[];         // [E]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x;
   const T* row = h + (size_t)t * dim;
-  if (given != nullptr) {            // the logits were formed by moe_logits_kernel
-    for (int e = lane; e < E; e += 32) z[e] = given[(size_t)t * E + e];
-  } else
-  for (int e = 0; e < E; ++e) {
-    const float* w = wr + (size_t)e * dim;
-    float s = 0.f;
-    for (int i = lane; i < dim; i += 32) s = fmaf(to_f32(row[i]), w[i], s);
-    s = warp_sum(s);
-    if (lane == 0) z[e] = s + (bias ? bias[e] : 0.f);
+  if (given != nullptr) {              // the logits were formed by moe_logits_kernel
+    for (int e = threadIdx.x; e < E; e += blockDim.x) z[e] = given[(size_t)t * E + e];
+  } else {
+    for (int e = warp; e < E; e += 8) {
+      const float* w = wr + (size_t)e * dim;
+      float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+      int i = lane;
+      for (; i + 96 < dim; i += 128) {
+        s0 = fmaf(to_f32(row[i]), w[i], s0);
+        s1 = fmaf(to_f32(row[i + 32]), w[i + 32], s1);
+        s2 = fmaf(to_f32(row[i + 64]), w[i + 64], s2);
+        s3 = fmaf(to_f32(row[i + 96]), w[i + 96], s3);
+      }
+      for (; i < dim; i += 32) s0 = fmaf(to_f32(row[i]), w[i], s0);
+      const float sum = warp_sum((s0 + s1) + (s2 + s3));
+      if (lane == 0) z[e] = sum + (bias ? bias[e] : 0.f);
+    }
   }
-  __syncwarp();
+  __syncthreads();
+  if (warp != 0) return;
   float first = 0.f, mass = 0.f;
   for (int k = 0; k < top; ++k) {
     float best = -INFINITY;
@@ -500,9 +519,8 @@ extern "C" int slb_moe_route(const void* h, const float* w_router, const float* 
   if (tokens == 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
   (void)rank;      // kept in the signature: callers hand over a table that older versions filled
-  const int warps = E <= 1024 ? 4 : 1;
-  const size_t smem = (size_t)warps * E * sizeof(float);
-  const dim3 grid((tokens + warps - 1) / warps), block(warps * 32);
+  const size_t smem = (size_t)E * sizeof(float);
+  const dim3 grid(tokens), block(256);
   // from a few tokens on the logits are formed 32 tokens and 16 experts at a time, each weight read once a block
   const float* given = nullptr;
   if (logits != nullptr && tokens >= 16) {
