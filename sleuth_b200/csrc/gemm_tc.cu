@@ -43,7 +43,32 @@ struct TcArgs {
   int M, N, K, ldc, mode;
   int up_row0;          // kTcSwiglu: first up row in W (= number of gate rows)
   int* status;          // 0 = fine; else a code saying which wait gave up
+  // Grouped form (one product per group of consecutive rows of X, each with a weight matrix of its own out of a
+  // stack): group_tiles[0] = number of row tiles, then per row tile (group, first row, rows). A row tile starts where
+  // its group's rows start, takes the group's matrix (rows group * group_w_rows .. of W) and stores only its own rows.
+  // Null: the plain product.
+  const int* group_tiles;
+  int group_w_rows;
 };
+
+// Where a tile lies: first row, one past the last row it may store, first row of its weights in W.
+struct TcTileAt {
+  int m0, m_end, w_row;
+};
+__device__ __forceinline__ TcTileAt tc_tile_at(const TcArgs& a, int tile, int m_tiles, int rows_per_tile, int rank, int n0) {
+  TcTileAt t;
+  if (a.group_tiles != nullptr) {
+    const int* g = a.group_tiles + 1 + 3 * (tile % m_tiles);
+    t.m0 = g[1];
+    t.m_end = g[1] + g[2];
+    t.w_row = g[0] * a.group_w_rows + n0;
+  } else {
+    t.m0 = (tile % m_tiles) * rows_per_tile + rank * kTcBM;
+    t.m_end = a.M;
+    t.w_row = n0;
+  }
+  return t;
+}
 
 // kTcQkv: what follows the fused q/k/v projection, done on the accumulator rows (float32) before anything is
 // rounded: bias, per-head RMSNorm of q and k, rotation of the whole head, and the store of q into [tokens, H, hd]
@@ -288,8 +313,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const bool gated = a.mode == kTcSwiglu;
   const int cols_per_tile = gated ? BN / 2 : BN;
-  const int m_tiles = (a.M + kRows - 1) / kRows, n_tiles = (a.N + cols_per_tile - 1) / cols_per_tile;
-  const int total = m_tiles * n_tiles;
+  int m_tiles = (a.M + kRows - 1) / kRows;
+  const int n_tiles = (a.N + cols_per_tile - 1) / cols_per_tile;
+  int total = m_tiles * n_tiles;
   const int k_tiles = (a.K + kTcBK - 1) / kTcBK;
 
   if (threadIdx.x == 0) {
@@ -322,6 +348,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   pdl_launch_dependents();
   pdl_wait();          // X is the previous kernel's output
   trace.mark(1);
+  if (a.group_tiles != nullptr) {      // the grouped form learns its row tiles from the kernel in front of it
+    m_tiles = a.group_tiles[0];
+    total = m_tiles * n_tiles;
+  }
 
   if (warp == 0) {
     if (lane == 0) {
@@ -329,7 +359,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       int it = 0;
       bool ok = true;
       for (int tile = worker; tile < total && ok; tile += n_workers) {
-        const int m0 = (tile % m_tiles) * kRows + (int)rank * kTcBM, n0 = (tile / m_tiles) * cols_per_tile;
+        const int n0 = (tile / m_tiles) * cols_per_tile;
+        const TcTileAt at = tc_tile_at(a, tile, m_tiles, kRows, (int)rank, n0);
+        const int m0 = at.m0;
         for (int kt = 0; kt < k_tiles; ++kt, ++it) {
           const int s = it % S;
           if (it >= S && !mbar_wait(empty0 + 8 * s, ((it / S) - 1) & 1)) {
@@ -349,9 +381,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
           } else {
             mbar_expect_tx(full0 + 8 * s, STAGE);
             tma_load_2d(sa, &map_x, kt * kTcBK, m0, full0 + 8 * s);
-            tma_load_2d(sb, &map_w, kt * kTcBK, n0, full0 + 8 * s);
-            if (gated) tma_load_2d(sb + B_BYTES / 2, &map_w, kt * kTcBK, a.up_row0 + n0, full0 + 8 * s);
-            else if (BN == 256) tma_load_2d(sb + B_BYTES / 2, &map_w, kt * kTcBK, n0 + 128, full0 + 8 * s);
+            tma_load_2d(sb, &map_w, kt * kTcBK, at.w_row, full0 + 8 * s);
+            if (gated) tma_load_2d(sb + B_BYTES / 2, &map_w, kt * kTcBK, a.up_row0 + at.w_row, full0 + 8 * s);
+            else if (BN == 256) tma_load_2d(sb + B_BYTES / 2, &map_w, kt * kTcBK, at.w_row + 128, full0 + 8 * s);
           }
         }
       }
@@ -411,7 +443,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     int t = 0;
     for (int tile = worker; tile < total; tile += n_workers, ++t) {
       const int buf = t & 1;
-      const int m0 = (tile % m_tiles) * kRows + (int)rank * kTcBM, n0 = (tile / m_tiles) * cols_per_tile;
+      const int n0 = (tile / m_tiles) * cols_per_tile;
+      const TcTileAt at = tc_tile_at(a, tile, m_tiles, kRows, (int)rank, n0);
+      const int m0 = at.m0;
       const int row = m0 + quad * 32 + lane;
       // Adding into the stream: the old values of this thread's row are fetched while the products still run, so
       // that the epilogue (which nothing hides when a block has a single tile) does not wait for them.
@@ -419,7 +453,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       float old[kPreload ? BN : 1];
       // (the whole warp or none of it: the tensor-memory loads are collective; a warp with rows beyond the matrix
       // takes the general path)
-      const bool preloaded = kPreload && __all_sync(0xffffffffu, a.mode == kTcAddF32 && row < a.M && n0 + BN <= a.N &&
+      const bool preloaded = kPreload && __all_sync(0xffffffffu, a.mode == kTcAddF32 && row < at.m_end && n0 + BN <= a.N &&
                                                                     (a.ldc % 8 == 0) && ((uintptr_t)a.C % 32 == 0));
       if constexpr (kPreload) {
         if (preloaded) {
@@ -482,7 +516,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
         }
-        if (row < a.M && n0 + c < a.N) store_row32(a, row, n0 + c, v);
+        if (row < at.m_end && n0 + c < a.N) store_row32(a, row, n0 + c, v);
       }
       // this warp has read its part of the accumulator: let the tensor core have the buffer back
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -635,6 +669,7 @@ extern "C" int slb_gemm_tc(const void* X, const void* W, void* C, int M, int N, 
   if (rc) return rc;
   TcArgs a;
   a.C = C; a.M = M; a.N = N; a.K = K; a.ldc = ldc; a.mode = mode; a.up_row0 = N; a.status = status;
+  a.group_tiles = nullptr; a.group_w_rows = 0;
   cudaStream_t s = (cudaStream_t)stream;
   if (pair) return bn == 256 ? launch_tc<256, false, true>(mx, mw, a, s) : launch_tc<128, false, true>(mx, mw, a, s);
   switch (bn) {
@@ -643,6 +678,33 @@ extern "C" int slb_gemm_tc(const void* X, const void* W, void* C, int M, int N, 
     case 64: return launch_tc<64>(mx, mw, a, s);
     default: return launch_tc<32>(mx, mw, a, s);
   }
+}
+
+// The grouped form: rows of X lie group by group (the groups' row tiles in `group_tiles`, written on the device by the
+// kernel in front: [0] = their number, then (group, first row, rows) each; at most `max_row_tiles` of them), W stacks
+// the groups' matrices (`w_rows` rows each: N, or 2 N for the gated form: gate rows then up rows), C [M, N] gets
+// each row's product with its own group's matrix. mode: 0 bfloat16, 1 float32, 3 gated activation.
+extern "C" int slb_gemm_tc_grouped(const void* X, const void* W, void* C, int M, int N, int K, int groups, int mode,
+                                   const int* group_tiles, int max_row_tiles, int* status, void* stream) {
+  SLB_REQUIRE(slb_gemm_tc_supported(M, N, K) && groups >= 1, "gemm_tc_grouped: M=%d N=%d K=%d groups=%d", M, N, K, groups);
+  SLB_REQUIRE((mode == 0 || mode == 1 || mode == 3) && status != nullptr && group_tiles != nullptr && max_row_tiles >= 1,
+              "gemm_tc_grouped: mode=%d", mode);
+  SLB_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0) && ((uintptr_t)C % 16 == 0),
+              "gemm_tc_grouped: X, W and C must be 16-byte aligned");
+  const bool gated = mode == kTcSwiglu;
+  const int w_rows = gated ? 2 * N : N;
+  const int bn = 256;                                   // many row tiles: the widest tile is the most efficient
+  CUtensorMap mx, mw;
+  int rc = make_map(&mx, X, M, K, kTcBM);
+  if (rc) return rc;
+  rc = make_map(&mw, W, (long long)groups * w_rows, K, 128);
+  if (rc) return rc;
+  TcArgs a;
+  a.C = C; a.N = N; a.K = K; a.ldc = N; a.mode = mode; a.up_row0 = N; a.status = status;
+  a.group_tiles = group_tiles; a.group_w_rows = w_rows;
+  a.M = max_row_tiles * kTcBM;                          // sizes the grid; the kernel reads the true number of row tiles
+  (void)bn;
+  return launch_tc<256>(mx, mw, a, (cudaStream_t)stream);
 }
 
 // The fused q/k/v projection of a step with many tokens: X [M, K] times W [(H + 2 * kv_heads) * head_dim, K]^T, and on
@@ -675,6 +737,7 @@ extern "C" int slb_gemm_tc_qkv(const void* X, const void* W, int M, int K, int h
   if (rc) return rc;
   TcArgs a;
   a.C = nullptr; a.M = M; a.N = N; a.K = K; a.ldc = N; a.mode = kTcQkv; a.up_row0 = N; a.status = status;
+  a.group_tiles = nullptr; a.group_w_rows = 0;
   TcQkv qa;
   qa.bias = bias; qa.q_gain = q_gain; qa.k_gain = k_gain; qa.cos_table = cos_table; qa.sin_table = sin_table;
   qa.q_out = (__nv_bfloat16*)q_out; qa.k_pool = (__nv_bfloat16*)k_pool; qa.v_pool = (__nv_bfloat16*)v_pool;

@@ -139,8 +139,11 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const T* __restrict__ h,
 // One block lays the pairs out expert by expert: counts[e], then place[pair] = first row of the pair's expert + the
 // pair's turn there, and list[place] = pair. The turns come from shared-memory counters, so which of an expert's rows
 // a pair gets may differ from run to run; every pair's result is computed from its own row alone, so nothing else does.
+// With `tiles`: also the experts' row tiles of `tile_rows` rows for the grouped product: [0] = their number, then
+// (expert, first row, rows) each.
 __global__ void __launch_bounds__(1024) moe_group_kernel(const int* __restrict__ choice, int* __restrict__ counts,
-                                                         int* __restrict__ place, int* __restrict__ list, int pairs, int E) {
+                                                         int* __restrict__ place, int* __restrict__ list, int pairs, int E,
+                                                         int* __restrict__ tiles, int tile_rows) {
   pdl_enter();
   extern __shared__ int sh[];          // [E] counts, then [E] first rows / cursors
   int* cnt = sh;
@@ -162,6 +165,18 @@ __global__ void __launch_bounds__(1024) moe_group_kernel(const int* __restrict__
       }
       if (e < E) cur[e] = run + inc - c;
       run += __shfl_sync(0xffffffffu, inc, 31);
+    }
+    __syncwarp();
+    if (tiles != nullptr && threadIdx.x == 0) {
+      int n = 0;
+      for (int e = 0; e < E; ++e)
+        for (int r = 0; r < cnt[e]; r += tile_rows) {
+          tiles[1 + 3 * n] = e;
+          tiles[2 + 3 * n] = cur[e] + r;
+          tiles[3 + 3 * n] = min(tile_rows, cnt[e] - r);
+          ++n;
+        }
+      tiles[0] = n;
     }
   }
   __syncthreads();
@@ -503,15 +518,72 @@ __global__ void moe_combine_kernel(float* __restrict__ x, const float* __restric
   }
 }
 
+// xs[r, :] = h[list[r] / top, :]: the tokens' rows in the expert order (16 bytes a lane).
+__global__ void moe_gather_kernel(const __nv_bfloat16* __restrict__ h, const int* __restrict__ list, __nv_bfloat16* __restrict__ xs,
+                                  int pairs, int dim, int top) {
+  pdl_enter();
+  const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (r >= pairs) return;
+  const uint4* src = reinterpret_cast<const uint4*>(h + (size_t)(list[r] / top) * dim);
+  uint4* dst = reinterpret_cast<uint4*>(xs + (size_t)r * dim);
+  for (int i = lane; i < dim / 8; i += 32) dst[i] = src[i];
+}
+
+// x[t, :] += sum over the token's choices, in their order, of weight[pair] * y[place[pair], :] (y in the expert order).
+__global__ void moe_combine_sorted_kernel(float* __restrict__ x, const float* __restrict__ y, const int* __restrict__ place,
+                                          const float* __restrict__ weight, int top, int dim, size_t total) {
+  pdl_enter();
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t step = (size_t)gridDim.x * blockDim.x;
+  for (; i < total; i += step) {
+    const size_t t = i / dim, d = i - t * dim;
+    float s = 0.f;
+    for (int k = 0; k < top; ++k) s = fmaf(weight[t * top + k], y[(size_t)place[t * top + k] * dim + d], s);
+    x[i] += s;
+  }
+}
+
 }  // namespace slb
 
 using namespace slb;
 
+extern "C" int slb_gemm_tc_grouped(const void* X, const void* W, void* C, int M, int N, int K, int groups, int mode,
+                                   const int* group_tiles, int max_row_tiles, int* status, void* stream);
+
+// The experts of a step of many pairs on the tcgen05 tensor cores (bfloat16, SiLU): the tokens' rows gathered into the
+// expert order (xs [pairs, dim]), the grouped product with the gated activation in its epilogue (act [pairs, ff]), the
+// grouped down product (y [pairs, dim] float32, expert order, unweighted), and the weighted sum into the stream.
+extern "C" int slb_moe_experts_tc(const void* h, const void* w_gu, const void* w_down, const int* list, const int* place,
+                                  const float* weight, const int* tiles, void* xs, void* act, float* y, float* x, int tokens,
+                                  int dim, int ff, int E, int top, int* status, void* stream) {
+  SLB_REQUIRE(tokens > 0 && dim > 0 && ff > 0 && E > 0 && top > 0 && dim % 8 == 0 && ff % 8 == 0,
+              "moe_experts_tc: tokens=%d dim=%d ff=%d experts=%d top=%d (inner sizes must be multiples of 8)", tokens, dim, ff, E, top);
+  SLB_REQUIRE(tiles != nullptr && status != nullptr, "moe_experts_tc: the row tiles and the status word are needed");
+  cudaStream_t s = (cudaStream_t)stream;
+  const long long pairs = (long long)tokens * top;
+  const long long max_tiles = pairs / 128 + (pairs < E ? pairs : E);
+  SLB_REQUIRE(pairs < (1LL << 30), "moe_experts_tc: too many pairs (%lld)", pairs);
+  launch(moe_gather_kernel, dim3((unsigned)((pairs + 7) / 8)), dim3(256), 0, s, (const __nv_bfloat16*)h, list, (__nv_bfloat16*)xs,
+         (int)pairs, dim, top);
+  int rc = check_launch("moe_gather");
+  if (rc) return rc;
+  rc = slb_gemm_tc_grouped(xs, w_gu, act, (int)pairs, ff, dim, E, 3, tiles, (int)max_tiles, status, stream);
+  if (rc) return rc;
+  rc = slb_gemm_tc_grouped(act, w_down, y, (int)pairs, dim, ff, E, 1, tiles, (int)max_tiles, status, stream);
+  if (rc) return rc;
+  const size_t total = (size_t)tokens * dim;
+  size_t blocks = (total + 255) / 256;
+  if (blocks > (size_t)sm_count() * 16) blocks = (size_t)sm_count() * 16;
+  launch(moe_combine_sorted_kernel, dim3((unsigned)blocks), dim3(256), 0, s, x, (const float*)y, place, weight, top, dim, total);
+  return check_launch("moe_combine");
+}
+
 // choice, place, list: int32 [tokens * top]; weight: float32 [tokens * top]; counts: int32 [E] (written here).
-// logits: float32 scratch [tokens, E], or null (then every token's warp forms its own logits).
+// logits: float32 scratch [tokens, E], or null (then every token's block forms its own logits). tiles: int32
+// [1 + 3 * (tokens * top / 128 + min(tokens * top, E))] for the grouped tensor-memory product, or null.
 extern "C" int slb_moe_route(const void* h, const float* w_router, const float* bias, int* choice, float* weight,
-                             int* rank, int* counts, int* place, int* list, float* logits, int tokens, int dim, int E,
-                             int top, int dtype, void* stream) {
+                             int* rank, int* counts, int* place, int* list, float* logits, int* tiles, int tokens, int dim,
+                             int E, int top, int dtype, void* stream) {
   SLB_REQUIRE(tokens >= 0 && dim > 0 && E > 0 && top > 0 && top <= E, "moe_route: tokens=%d dim=%d experts=%d top=%d",
               tokens, dim, E, top);
   SLB_REQUIRE(E <= 4096, "moe_route: at most 4096 experts, got %d", E);
@@ -540,7 +612,7 @@ extern "C" int slb_moe_route(const void* h, const float* w_router, const float* 
   if (rc) return rc;
   const int pairs = tokens * top;
   launch(moe_group_kernel, dim3(1), dim3(pairs >= 1024 ? 1024 : 256), 2 * sizeof(int) * E, s, (const int*)choice, counts, place, list,
-         pairs, E);
+         pairs, E, tiles, 128);
   return check_launch("moe_group");
 }
 

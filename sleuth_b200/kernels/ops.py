@@ -748,12 +748,19 @@ def latent_gate(val, g, y, stream=None) -> None:
 
 
 # ---- routed experts (csrc/moe.cu) ----
-def moe_route(h, w_router, bias, choice, weight, rank, counts, place, order, top: int, stream=None, logits=None) -> None:
+def moe_tile_words(tokens: int, top: int, experts: int) -> int:
+    """int32 words of the row-tile table that ``moe_route`` writes for ``moe_experts_tc``."""
+    pairs = tokens * top
+    return 1 + 3 * (pairs // 128 + min(pairs, experts))
+
+
+def moe_route(h, w_router, bias, choice, weight, rank, counts, place, order, top: int, stream=None, logits=None,
+              tiles=None) -> None:
     """Router logits in float32, the ``top`` largest per token, softmax over those; then the (token, choice) pairs are
     laid out expert by expert: counts [experts], place [T * top] (a pair's row in that order), order [T * top] (the
     pair at each row). choice, rank int32 [T * top]; weight float32 [T * top]. ``logits``: float32 scratch
     [T, experts]; with it, steps of many tokens form their logits 32 tokens at a time (the same sums, k ascending)."""
-    _cuda(h, w_router, bias, choice, weight, rank, counts, place, order, logits)
+    _cuda(h, w_router, bias, choice, weight, rank, counts, place, order, logits, tiles)
     T, d = h.shape
     E = w_router.shape[0]
     _need(h.dtype in DT and w_router.dtype == torch.float32 and w_router.shape == (E, d), "moe_route: input or router matrix")
@@ -763,8 +770,9 @@ def moe_route(h, w_router, bias, choice, weight, rank, counts, place, order, top
     _need(weight.dtype == torch.float32 and weight.numel() >= T * top and counts.dtype == torch.int32 and counts.numel() >= E,
           "moe_route: weights or counts")
     _need(logits is None or (logits.dtype == torch.float32 and logits.numel() >= T * E), "moe_route: scratch for the logits")
+    _need(tiles is None or (tiles.dtype == torch.int32 and tiles.numel() >= moe_tile_words(T, top, E)), "moe_route: row-tile table")
     lib().call("slb_moe_route", _p(h), _p(w_router), _p(bias), _p(choice), _p(weight), _p(rank), _p(counts), _p(place),
-               _p(order), _p(logits), T, d, E, int(top), DT[h.dtype], stream if stream is not None else current_stream())
+               _p(order), _p(logits), _p(tiles), T, d, E, int(top), DT[h.dtype], stream if stream is not None else current_stream())
 
 
 def moe_experts(h, w_gate_up, w_down, counts, order, weight, act, y, x, top: int, activation: str = "silu",
@@ -785,4 +793,24 @@ def moe_experts(h, w_gate_up, w_down, counts, order, weight, act, y, x, top: int
     _need(activation in ACTIVATIONS, f"moe_experts: activation {activation!r}")
     lib().call("slb_moe_experts", _p(h), _p(w_gate_up), _p(w_down), _p(counts), _p(order), _p(choice), _p(place), _p(weight), _p(act), _p(y),
                _p(x), T, d, ff, E, int(top), ACTIVATIONS[activation], DT[h.dtype],
+               stream if stream is not None else current_stream())
+
+
+def moe_experts_tc(h, w_gate_up, w_down, order, place, weight, tiles, xs, act, y, x, top: int, stream=None) -> None:
+    """The same sum as ``moe_experts`` for steps of many pairs, bfloat16 and SiLU: the tokens' rows gathered into the
+    expert order (``xs`` [T * top, d]) and both products as grouped tcgen05 products over the row tiles that
+    ``moe_route`` wrote into ``tiles``; ``y`` [T * top, d] float32 comes out in the expert order."""
+    _cuda(h, w_gate_up, w_down, order, place, weight, tiles, xs, act, y, x)
+    T, d = h.shape
+    E, ff2, _ = w_gate_up.shape
+    ff = ff2 // 2
+    _need(w_gate_up.shape == (E, 2 * ff, d) and w_down.shape == (E, d, ff), "moe_experts_tc: expert matrices")
+    _need(h.dtype == w_gate_up.dtype == w_down.dtype == act.dtype == xs.dtype == torch.bfloat16, "moe_experts_tc: bfloat16 only")
+    _need(d % 8 == 0 and ff % 8 == 0, "moe_experts_tc: inner sizes must be multiples of 8")
+    _need(xs.shape == (T * top, d) and act.shape == (T * top, ff) and y.shape == (T * top, d) and y.dtype == torch.float32,
+          "moe_experts_tc: scratch")
+    _need(x.shape == (T, d) and x.dtype == torch.float32, "moe_experts_tc: the stream")
+    _need(tiles.dtype == torch.int32 and tiles.numel() >= moe_tile_words(T, top, E), "moe_experts_tc: row-tile table")
+    lib().call("slb_moe_experts_tc", _p(h), _p(w_gate_up), _p(w_down), _p(order), _p(place), _p(weight), _p(tiles), _p(xs),
+               _p(act), _p(y), _p(x), T, d, ff, E, int(top), _p(_tc_status(h.device)),
                stream if stream is not None else current_stream())

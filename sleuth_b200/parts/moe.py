@@ -7,7 +7,8 @@ and an expert is down(act(gate h) * (up h)). The part's output, the weighted sum
 The experts' matrices are stacked at load time ([experts, 2 * ff, hidden] for gate and up, [experts, hidden, ff]
 for down). A step runs five kernels (``csrc/moe.cu``): router, the counts and the expert-ordered list of (token,
 choice) pairs, gate/up with the activation, down scaled by the pair's weight, and the sum over a token's choices
-in the order of the choices. None of them needs the host to know the counts, so the part can be recorded in a
+in the order of the choices; bfloat16 steps of many pairs gather the tokens' rows into the expert order and run both
+products as grouped tcgen05 products instead (``ops.moe_experts_tc``). None of them needs the host to know the counts, so the part can be recorded in a
 CUDA graph like any other.
 """
 
@@ -18,6 +19,11 @@ import torch
 from ..kernels import ops
 from .base import BuildContext, Normed, ParamDecl, Part, register_ffn
 from .spec import RoutedExpertsSpec
+
+
+# From this many (token, choice) pairs on a bfloat16 step runs its experts as grouped tcgen05 products (row tiles of 128
+# pairs an expert); below, the warp-level kernels, whose tiles of 64 rows waste less on experts with few pairs.
+TC_PAIRS = 1024
 
 
 class RoutedExperts(Part):
@@ -61,9 +67,17 @@ class RoutedExperts(Part):
         act = ws.take((pairs, s.intermediate), dt)
         y = ws.take((pairs, s.hidden), torch.float32)
         logits = ws.take((T, s.experts), torch.float32)
-        ops.moe_route(h, self.w_router, self.bias, choice, weight, rank, counts, place, order, s.top, b.stream, logits)
-        ops.moe_experts(h, self.w_gate_up, self.w_down, counts, order, weight, act, y, x, s.top, s.activation, b.stream,
-                        choice, place)
+        # steps of many pairs: the tcgen05 grouped products (bfloat16, SiLU, inner sizes that TMA takes)
+        grouped = (dt == torch.bfloat16 and s.activation == "silu" and pairs >= TC_PAIRS and s.hidden % 8 == 0
+                   and s.intermediate % 8 == 0)
+        tiles = ws.take((ops.moe_tile_words(T, s.top, s.experts),), torch.int32) if grouped else None
+        ops.moe_route(h, self.w_router, self.bias, choice, weight, rank, counts, place, order, s.top, b.stream, logits, tiles)
+        if grouped:
+            xs = ws.take((pairs, s.hidden), dt)
+            ops.moe_experts_tc(h, self.w_gate_up, self.w_down, order, place, weight, tiles, xs, act, y, x, s.top, b.stream)
+        else:
+            ops.moe_experts(h, self.w_gate_up, self.w_down, counts, order, weight, act, y, x, s.top, s.activation, b.stream,
+                            choice, place)
         ws.release(mark)
 
 

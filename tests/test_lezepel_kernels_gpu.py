@@ -206,7 +206,7 @@ def expert_weights(E, d, ff, seed, dtype):
 
 @pytest.mark.parametrize("dtype", ["fp32", "bf16"])
 @pytest.mark.parametrize("T, d, ff, E, top", [(1, 72, 36, 5, 2), (77, 72, 20, 6, 1), (300, 256, 96, 16, 4), (40, 64, 16, 4, 4),
-                                              (9, 50, 33, 70, 3)])
+                                              (9, 50, 33, 70, 3), (700, 128, 200, 7, 3), (3, 64, 136, 5, 2)])
 def test_router_and_experts(T, d, ff, E, top, dtype):
     o, dt = ops(), DT[dtype]
     w = expert_weights(E, d, ff, T, dtype)
@@ -238,6 +238,19 @@ def test_router_and_experts(T, d, ff, E, top, dtype):
     x2 = x0.clone().to(DEV)          # and through the tiles whatever the number of pairs
     o.moe_experts(h.to(DEV), gu, dn, counts, order, weight, act, y, x2, top, "silu")
     torch.testing.assert_close(x2, x, **TOL[dtype])
+    if dtype == "bf16" and d % 8 == 0 and ff % 8 == 0:      # and as grouped tensor-memory products over the experts' row tiles
+        tiles = torch.empty(o.moe_tile_words(T, top, E), dtype=torch.int32, device=DEV)
+        o.moe_route(h.to(DEV), w["router"].to(DEV), w["router.b"].to(DEV), choice, weight, rank, counts, place, order, top,
+                    logits=logits, tiles=tiles)
+        n = int(tiles[0])
+        table = tiles[1:1 + 3 * n].view(n, 3).cpu()
+        assert int(table[:, 2].sum()) == pairs and int(table[:, 2].max()) <= 128
+        x3 = x0.clone().to(DEV)
+        xs = torch.empty(pairs, d, dtype=dt, device=DEV)
+        o.moe_experts_tc(h.to(DEV), gu, dn, order, place, weight, tiles, xs, act, y, x3, top)
+        torch.cuda.synchronize()
+        o.gemm_tc_check(torch.device(DEV))
+        torch.testing.assert_close(x3, x, **TOL[dtype])
     want = x0.double() + plain.routed_experts(h.double(), {k: v.double() for k, v in w.items()}, "", {"router": {"experts": E, "top": top}})
     torch.testing.assert_close(x.cpu().double(), want, **TOL[dtype])
 
