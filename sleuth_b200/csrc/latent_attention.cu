@@ -13,6 +13,8 @@
 //                         arithmetic; the rotation of the query's rotated part happens as the queries are loaded;
 //                         a long sequence's keys may be cut into slices whose partial results latent_merge_kernel joins
 //   latent_attn_mma_kernel  the same on the warp-level tensor cores (bfloat16, widths that are multiples of 16)
+//   head_prompt_mma_kernel  whole prompts (every sequence starts at 0): per-head keys and values formed from the step's
+//                         latents by one product, then ordinary causal attention per head on the tensor cores
 //   latent_gate_kernel    y[t, h, :] = value[h, t, :] * sigmoid(g[t, h, :])
 #include "mma_sync.cuh"
 
@@ -30,7 +32,7 @@ __global__ void latent_post_kernel(const float* __restrict__ lat, const float* _
                                    const float* __restrict__ sin_t, TO* __restrict__ cq, TO* __restrict__ pool,
                                    const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
                                    const int* __restrict__ table, int stride, int q_rank, int R, int P, int rot,
-                                   float eps) {
+                                   float eps, TO* __restrict__ c_out, TO* __restrict__ k_out) {
   pdl_enter();
   __shared__ float scratch[33];
   const int t = blockIdx.x;
@@ -44,11 +46,18 @@ __global__ void latent_post_kernel(const float* __restrict__ lat, const float* _
   const float inv_c = 1.0f / sqrtf(sc / (float)R + eps);
   TO* qo = cq + (size_t)t * q_rank;
   for (int i = threadIdx.x; i < q_rank; i += blockDim.x) qo[i] = from_f32<TO>((row[i] * inv_q) * q_gain[i]);
-  if (pool == nullptr) return;
+  if (pool == nullptr && c_out == nullptr) return;
   const int pos = tok_pos[t];
-  const int page = table[(size_t)tok_seq[t] * stride + pos / kPageTokens];
-  TO* dst = pool + ((size_t)page * kPageTokens + pos % kPageTokens) * (R + P);
-  for (int i = threadIdx.x; i < R; i += blockDim.x) dst[i] = from_f32<TO>((row[q_rank + i] * inv_c) * c_gain[i]);
+  TO* dst = nullptr;
+  if (pool != nullptr) {
+    const int page = table[(size_t)tok_seq[t] * stride + pos / kPageTokens];
+    dst = pool + ((size_t)page * kPageTokens + pos % kPageTokens) * (R + P);
+  }
+  for (int i = threadIdx.x; i < R; i += blockDim.x) {
+    const TO v = from_f32<TO>((row[q_rank + i] * inv_c) * c_gain[i]);
+    if (dst) dst[i] = v;
+    if (c_out) c_out[(size_t)t * R + i] = v;      // the same values side by side, for products over the step's own tokens
+  }
   const float* kr = row + q_rank + R;
   const int half = rot / 2;
   for (int i = threadIdx.x; i < P; i += blockDim.x) {
@@ -58,7 +67,8 @@ __global__ void latent_post_kernel(const float* __restrict__ lat, const float* _
       const float c = cos_t[(size_t)pos * half + f], s = sin_t[(size_t)pos * half + f];
       v = i < half ? kr[i] * c - kr[i + half] * s : kr[i] * c + kr[i - half] * s;
     }
-    dst[R + i] = from_f32<TO>(v);
+    if (dst) dst[R + i] = from_f32<TO>(v);
+    if (k_out) k_out[(size_t)t * P + i] = from_f32<TO>(v);
   }
 }
 
@@ -498,6 +508,206 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(const LatentAttnAr
   }
 }
 
+// ---- whole prompts: attention with per-head keys and values (bfloat16) ----
+// When every sequence of a step starts at position 0 its keys are the step's own tokens, and forming each head's
+// unrotated key and value from the latents (one product for all tokens) costs little beside an attention that then
+// multiplies d_n + d_r + d_v instead of r + d_r + r values per head and pair of tokens. Block: 64 query rows of one
+// (sequence, head) on four warps; the query fragments stay in registers (the rotated part is turned as it is loaded);
+// 64 keys a step in shared memory: the head's unrotated key values and the shared rotated part side by side, and the
+// head's values; mma.sync m16n8k16, float32 sums, online softmax in registers.
+struct HeadPromptArgs {
+  const __nv_bfloat16* q;        // [T, H, dn + P] up-projected queries, rotated part not yet turned
+  const __nv_bfloat16* kv;       // [T, H * dn + H * dv]: every head's unrotated key values, then every head's values
+  const __nv_bfloat16* k_rot;    // [T, P] the shared key part, turned
+  __nv_bfloat16* out;            // [H, T, dv]
+  const float* cos_t;
+  const float* sin_t;
+  const int* seq_start;
+  const int* counts;
+  int T, H, dn, P, dv, rot, window;
+  float scale;
+};
+
+template <int KQ, int NV>       // at most KQ * 16 key values and NV * 16 value columns a head
+__global__ void __launch_bounds__(128) head_prompt_mma_kernel(const HeadPromptArgs a) {
+  pdl_enter();
+  extern __shared__ __align__(16) unsigned char hp_raw[];
+  const int DK = a.dn + a.P, ksd = DK + 8, vsd = a.dv + 8;
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(hp_raw);   // [64][ksd]
+  __nv_bfloat16* Ks = Qs + 64 * ksd;                              // two buffers of [64][ksd]
+  __nv_bfloat16* Vs = Ks + 128 * ksd;                             // two buffers of [64][vsd]
+  const int seq = blockIdx.y, h = blockIdx.z;
+  const int count = a.counts[seq];
+  const int n_tiles = (count + 63) / 64;
+  const int tile = n_tiles - 1 - (int)blockIdx.x;                 // the long tiles first
+  if (tile < 0) return;
+  const int r0 = tile * 64;
+  const int tok0 = a.seq_start[seq];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t4 = lane & 3;
+  const int half = a.rot / 2;
+  const int kv_stride = a.H * (a.dn + a.dv);
+  // queries of rows r0 .. r0 + 63 (positions = rows: the sequences start at 0)
+  for (int r = warp; r < 64; r += 4) {
+    __nv_bfloat16* qs = Qs + r * ksd;
+    const int pos = r0 + r;
+    if (pos >= count) {
+      for (int i = lane * 8; i < DK; i += 256) *reinterpret_cast<uint4*>(qs + i) = make_uint4(0, 0, 0, 0);
+      continue;
+    }
+    const __nv_bfloat16* src = a.q + ((size_t)(tok0 + pos) * a.H + h) * DK;
+    for (int i = lane; i < a.dn; i += 32) qs[i] = src[i];
+    const __nv_bfloat16* qr = src + a.dn;
+    for (int i = lane; i < a.P; i += 32) {
+      float v = __bfloat162float(qr[i]);
+      if (i < a.rot) {
+        const int f = i < half ? i : i - half;
+        const float c = a.cos_t[(size_t)pos * half + f], sn = a.sin_t[(size_t)pos * half + f];
+        v = i < half ? v * c - __bfloat162float(qr[i + half]) * sn : v * c + __bfloat162float(qr[i - half]) * sn;
+      }
+      qs[a.dn + i] = __float2bfloat16_rn(v);
+    }
+  }
+  __syncthreads();
+  const int kq = DK / 16, nv = a.dv / 16;
+  uint32_t qf[KQ][4];
+#pragma unroll
+  for (int kb = 0; kb < KQ; ++kb)
+    if (kb < kq) ldmatrix_x4(qf[kb], smem_u32(Qs) + 2 * ((warp * 16 + (lane & 15)) * ksd + kb * 16 + ((lane >> 4) << 3)));
+  int pos_r[2], lo_r[2];
+#pragma unroll
+  for (int hh = 0; hh < 2; ++hh) {
+    const int p = r0 + warp * 16 + g + 8 * hh;
+    pos_r[hh] = p < count ? p : -1;
+    lo_r[hh] = a.window > 0 ? max(0, p - a.window + 1) : 0;
+  }
+  const bool warp_active = r0 + warp * 16 < count;
+  const int last_pos = min(count, r0 + 64) - 1;
+  const int key_lo = (a.window > 0 ? max(0, r0 - a.window + 1) : 0) / 64 * 64;
+  float o[2 * NV][4];
+#pragma unroll
+  for (int i = 0; i < 2 * NV; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m_r[2] = {-INFINITY, -INFINITY}, l_r[2] = {0.f, 0.f};
+  const float scale_log2 = a.scale * 1.4426950408889634f;
+  const int kp = a.dn / 8, rp = a.P / 8, vp = a.dv / 8;
+  // 64 keys into buffer `buf`: the head's unrotated key values and the shared rotated part side by side, and its values
+  auto load_keys = [&](int k0, int buf) {
+    const int nk = min(64, last_pos - k0 + 1);
+    __nv_bfloat16* kb = Ks + buf * 64 * ksd;
+    __nv_bfloat16* vb = Vs + buf * 64 * vsd;
+    for (int i = tid; i < 64 * (kp + rp + vp); i += 128) {
+      const int j = i / (kp + rp + vp), p = i - j * (kp + rp + vp);
+      __nv_bfloat16* dst;
+      const __nv_bfloat16* src;
+      const size_t tok = (size_t)(tok0 + k0 + j);
+      if (p < kp) { dst = kb + j * ksd + p * 8; src = a.kv + tok * kv_stride + h * a.dn + p * 8; }
+      else if (p < kp + rp) { dst = kb + j * ksd + a.dn + (p - kp) * 8; src = a.k_rot + tok * a.P + (p - kp) * 8; }
+      else { dst = vb + j * vsd + (p - kp - rp) * 8; src = a.kv + tok * kv_stride + a.H * a.dn + h * a.dv + (p - kp - rp) * 8; }
+      if (j < nk) cp_async16(smem_u32(dst), src);
+      else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+    }
+    cp_async_commit();
+  };
+
+  load_keys(key_lo, 0);
+  int buf = 0;
+  for (int k0 = key_lo; k0 <= last_pos; k0 += 64, buf ^= 1) {
+    if (k0 + 64 <= last_pos) {        // the next 64 keys are on their way while these are multiplied
+      load_keys(k0 + 64, buf ^ 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const uint32_t k_base = smem_u32(Ks + buf * 64 * ksd), v_base = smem_u32(Vs + buf * 64 * vsd);
+    if (warp_active && k0 <= r0 + warp * 16 + 15) {       // else: keys after all of this warp's rows
+    float s[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+#pragma unroll
+    for (int kb = 0; kb < KQ; ++kb) {
+      if (kb < kq) {
+#pragma unroll
+        for (int jp = 0; jp < 4; ++jp) {
+          uint32_t kf[4];
+          ldmatrix_x4(kf, k_base + 2 * ((jp * 16 + (lane & 7) + ((lane >> 4) << 3)) * ksd + kb * 16 + (((lane >> 3) & 1) << 3)));
+          mma_bf16(s[2 * jp], qf[kb], kf[0], kf[1]);
+          mma_bf16(s[2 * jp + 1], qf[kb], kf[2], kf[3]);
+        }
+      }
+    }
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int hh = e >> 1;
+        const int key = k0 + j * 8 + 2 * t4 + (e & 1);
+        float v = s[j][e] * scale_log2;
+        if (key > pos_r[hh] || key < lo_r[hh]) v = -INFINITY;
+        s[j][e] = v;
+        mx[hh] = fmaxf(mx[hh], v);
+      }
+    }
+    float alpha[2], m_use[2];
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      mx[hh] = fmaxf(mx[hh], __shfl_xor_sync(0xffffffffu, mx[hh], 1));
+      mx[hh] = fmaxf(mx[hh], __shfl_xor_sync(0xffffffffu, mx[hh], 2));
+      const float m_new = fmaxf(m_r[hh], mx[hh]);
+      m_use[hh] = m_new == -INFINITY ? 0.f : m_new;
+      alpha[hh] = exp2f(m_r[hh] - m_use[hh]);
+      m_r[hh] = m_new;
+    }
+    float sum[2] = {0.f, 0.f};
+    uint32_t pf[4][4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float p0 = exp2f(s[j][0] - m_use[0]), p1 = exp2f(s[j][1] - m_use[0]);
+      const float p2 = exp2f(s[j][2] - m_use[1]), p3 = exp2f(s[j][3] - m_use[1]);
+      sum[0] += p0 + p1;
+      sum[1] += p2 + p3;
+      pf[j >> 1][(j & 1) * 2 + 0] = pack_bf16(p0, p1);
+      pf[j >> 1][(j & 1) * 2 + 1] = pack_bf16(p2, p3);
+    }
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) l_r[hh] = l_r[hh] * alpha[hh] + sum[hh];
+#pragma unroll
+    for (int i = 0; i < 2 * NV; ++i) {
+      o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
+      o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+    }
+#pragma unroll
+    for (int kb = 0; kb < 4; ++kb) {
+#pragma unroll
+      for (int dp = 0; dp < NV; ++dp) {
+        if (dp < nv) {
+          uint32_t vf[4];
+          ldmatrix_x4_trans(vf, v_base + 2 * ((kb * 16 + (lane & 15)) * vsd + dp * 16 + ((lane >> 4) << 3)));
+          mma_bf16(o[2 * dp], pf[kb], vf[0], vf[1]);
+          mma_bf16(o[2 * dp + 1], pf[kb], vf[2], vf[3]);
+        }
+      }
+    }
+    }
+    __syncthreads();      // this buffer is the target of the next iteration's fetch
+  }
+#pragma unroll
+  for (int hh = 0; hh < 2; ++hh) {
+    l_r[hh] += __shfl_xor_sync(0xffffffffu, l_r[hh], 1);
+    l_r[hh] += __shfl_xor_sync(0xffffffffu, l_r[hh], 2);
+  }
+#pragma unroll
+  for (int hh = 0; hh < 2; ++hh) {
+    if (pos_r[hh] < 0) continue;
+    const float inv = l_r[hh] > 0.f ? 1.0f / l_r[hh] : 0.f;
+    __nv_bfloat16* dst = a.out + ((size_t)h * a.T + tok0 + pos_r[hh]) * a.dv;
+#pragma unroll
+    for (int i = 0; i < 2 * NV; ++i)
+      if ((i >> 1) < nv)
+        *reinterpret_cast<uint32_t*>(dst + i * 8 + 2 * t4) = pack_bf16(o[i][2 * hh] * inv, o[i][2 * hh + 1] * inv);
+  }
+}
+
 // One block per (token, head): the slices' factors exp(m_s - m) / mass are formed once, then every thread joins its
 // columns over the slices in slice order.
 template <typename T>
@@ -579,7 +789,7 @@ using namespace slb;
 extern "C" int slb_latent_post(const float* lat, const float* q_gain, const float* c_gain, const float* cos_t,
                                const float* sin_t, void* cq, void* pool, const int* tok_seq, const int* tok_pos,
                                const int* table, int stride, int tokens, int q_rank, int R, int P, int rot, float eps,
-                               int dtype, void* stream) {
+                               int dtype, void* c_out, void* k_out, void* stream) {
   SLB_REQUIRE(tokens >= 0 && q_rank > 0 && R > 0 && P >= 0 && rot >= 0 && rot <= P && rot % 2 == 0 && eps > 0.f,
               "latent_post: tokens=%d q_rank=%d rank=%d rot_dim=%d rotated=%d", tokens, q_rank, R, P, rot);
   SLB_REQUIRE(dtype == kF32 || dtype == kBF16, "latent_post: unknown dtype %d", dtype);
@@ -589,10 +799,11 @@ extern "C" int slb_latent_post(const float* lat, const float* q_gain, const floa
   const int threads = widest > 512 ? 256 : (widest > 128 ? 128 : 64);
   if (dtype == kF32)
     launch(latent_post_kernel<float>, dim3(tokens), dim3(threads), 0, s, lat, q_gain, c_gain, cos_t, sin_t, (float*)cq,
-           (float*)pool, tok_seq, tok_pos, table, stride, q_rank, R, P, rot, eps);
+           (float*)pool, tok_seq, tok_pos, table, stride, q_rank, R, P, rot, eps, (float*)c_out, (float*)k_out);
   else
     launch(latent_post_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), 0, s, lat, q_gain, c_gain, cos_t, sin_t,
-           (__nv_bfloat16*)cq, (__nv_bfloat16*)pool, tok_seq, tok_pos, table, stride, q_rank, R, P, rot, eps);
+           (__nv_bfloat16*)cq, (__nv_bfloat16*)pool, tok_seq, tok_pos, table, stride, q_rank, R, P, rot, eps, (__nv_bfloat16*)c_out,
+           (__nv_bfloat16*)k_out);
   return check_launch("latent_post");
 }
 
@@ -696,6 +907,49 @@ extern "C" int slb_latent_attention(const void* q_lat, const void* q_raw, const 
     launch(latent_merge_kernel<__nv_bfloat16>, dim3(rows), dim3(128), 0, s, (const float*)parts,
            (__nv_bfloat16*)out, rows, T, H, R, splits);
   return check_launch("latent_merge");
+}
+
+// Whether the per-head prompt kernel takes these head sizes (bfloat16 only).
+extern "C" int slb_head_prompt_supported(int dn, int P, int dv) {
+  const int DK = dn + P;
+  return dn > 0 && dv > 0 && dn % 8 == 0 && P % 8 == 0 && DK % 16 == 0 && dv % 16 == 0 && DK <= 256 && dv <= 256 ? 1 : 0;
+}
+
+// Attention of whole prompts (every sequence starts at position 0) with per-head keys and values; see HeadPromptArgs.
+extern "C" int slb_head_prompt_attention(const void* q, const void* kv, const void* k_rot, void* out, const float* cos_t,
+                                         const float* sin_t, const int* seq_start, const int* counts, int n_seqs,
+                                         int max_count, int T, int H, int dn, int P, int dv, int rot, int window,
+                                         float scale, void* stream) {
+  SLB_REQUIRE(slb_head_prompt_supported(dn, P, dv), "head_prompt_attention: head sizes %d + %d, %d are not taken", dn, P, dv);
+  SLB_REQUIRE(n_seqs >= 0 && max_count >= 0 && T >= 0 && H > 0 && rot >= 0 && rot <= P && rot % 2 == 0 && window >= 0,
+              "head_prompt_attention: seqs=%d max=%d heads=%d", n_seqs, max_count, H);
+  SLB_REQUIRE((((uintptr_t)q | (uintptr_t)kv | (uintptr_t)k_rot | (uintptr_t)out) % 16 == 0) && (H * (dn + dv)) % 8 == 0,
+              "head_prompt_attention: 16-byte alignment");
+  if (n_seqs == 0 || max_count == 0 || T == 0) return 0;
+  HeadPromptArgs a;
+  a.q = (const __nv_bfloat16*)q; a.kv = (const __nv_bfloat16*)kv; a.k_rot = (const __nv_bfloat16*)k_rot;
+  a.out = (__nv_bfloat16*)out; a.cos_t = cos_t; a.sin_t = sin_t; a.seq_start = seq_start; a.counts = counts;
+  a.T = T; a.H = H; a.dn = dn; a.P = P; a.dv = dv; a.rot = rot; a.window = window; a.scale = scale;
+  const size_t smem = (size_t)(192 * (dn + P + 8) + 128 * (dv + 8)) * 2;
+  const dim3 grid((max_count + 63) / 64, n_seqs, H), block(128);
+  cudaStream_t s = (cudaStream_t)stream;
+  const int kq = (dn + P) / 16, nv = dv / 16;
+#define SLB_HP(KQ, NV)                                                                                          \
+  do {                                                                                                          \
+    static bool raised = false;                                                                                 \
+    if (!raised) {                                                                                              \
+      cudaFuncSetAttribute(head_prompt_mma_kernel<KQ, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kLatMaxSmem); \
+      raised = true;                                                                                            \
+    }                                                                                                           \
+    launch(head_prompt_mma_kernel<KQ, NV>, grid, block, smem, s, a);                                            \
+  } while (0)
+  if (kq <= 8) {
+    if (nv <= 4) SLB_HP(8, 4); else if (nv <= 8) SLB_HP(8, 8); else SLB_HP(8, 16);
+  } else {
+    if (nv <= 4) SLB_HP(16, 4); else if (nv <= 8) SLB_HP(16, 8); else SLB_HP(16, 16);
+  }
+#undef SLB_HP
+  return check_launch("head_prompt_attention");
 }
 
 extern "C" int slb_latent_gate(const void* val, const void* g, void* y, int tokens, int H, int dv, int dtype,

@@ -45,6 +45,7 @@ class StepBatch:
     host_slots: list = field(default_factory=list)
     max_count: int = 1
     max_len: int = 0
+    fresh: bool = False         # every sequence of the step starts at position 0: its keys are the step's own tokens
     # the weight matrix that is read right after the part now running has finished (the next part's first product),
     # or None: the last kernel of a part may ask the L2 cache for it
     next_read: torch.Tensor | None = None
@@ -180,4 +181,5 @@ class MetaStager:
             slots=view("slots"), rows=view("rows"),
             tables=[view(f"table{g}").view(n, self.stride) for g in range(self.n_groups)], floats=fl,
             host_counts=list(map(int, counts)), host_past=list(map(int, pasts)), host_slots=list(map(int, slots)),
-            max_count=int(counts_a.max()) if n else 0, max_len=int((pasts_a + counts_a).max()) if n else 0)
+            max_count=int(counts_a.max()) if n else 0, max_len=int((pasts_a + counts_a).max()) if n else 0,
+            fresh=bool(n) and not bool(pasts_a.any()))

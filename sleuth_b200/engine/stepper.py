@@ -219,7 +219,7 @@ class Stepper:
         if not (self.use_graphs and getattr(self.model, "capturable", True) and 0 < W <= self.max_graph_rows):
             return False
         self._check_graph_key()
-        gkey = ("chunk", b.T, b.n, b.max_count, W)
+        gkey = ("chunk", b.T, b.n, b.max_count, W, b.fresh)      # parts may treat steps that start at position 0 differently
         graph = self._graphs.get(gkey)
         if graph is None and gkey not in self._seen_chunk:
             self._seen_chunk.add(gkey)

@@ -152,7 +152,8 @@ _SIGNATURES = {
     "slb_sample": [P, L, I, I, F, I, F, F, P, P, P],
     "slb_gated_act": [P, P, I, I, I, I, P],
     "slb_stream_inject": [P, P, P, I, I, P],
-    "slb_latent_post": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, P],
+    "slb_latent_post": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, P, P, P],
+    "slb_head_prompt_attention": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P],
     "slb_latent_attention": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, I, P],
     "slb_latent_gate": [P, P, P, I, I, I, I, P],
     "slb_moe_route": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, P],

@@ -662,12 +662,17 @@ def sample(logits: torch.Tensor, limit: int, temperature: float, top_k: int, top
 
 # ---- attention through low-rank latents (csrc/latent_attention.cu) ----
 def latent_post(lat, q_gain, c_gain, cos, sin, cq, pool, tok_seq, tok_pos, block_table, q_rank: int, rank: int,
-                rot_dim: int, rotated: int, eps: float, stream=None) -> None:
+                rot_dim: int, rotated: int, eps: float, stream=None, c_out=None, k_out=None) -> None:
     """lat [T, q_rank + rank + rot_dim] float32 (the two down-projections' output): the normed query latent goes to
     ``cq`` [T, q_rank]; the normed latent and the rotated key part go to the token's row of ``pool``
     [pages, 64, rank + rot_dim] (``pool`` None: nothing is stored). ``rotated``: how many leading channels of the key
-    part turn."""
-    _cuda(lat, q_gain, c_gain, cos, sin, cq, pool, tok_seq, tok_pos, block_table)
+    part turn. ``c_out`` [T, rank] and ``k_out`` [T, rot_dim]: the same latent and key part once more, side by side in
+    the order of the step's tokens (for a step that multiplies its own tokens' latents)."""
+    _cuda(lat, q_gain, c_gain, cos, sin, cq, pool, tok_seq, tok_pos, block_table, c_out, k_out)
+    _need((c_out is None) == (k_out is None), "latent_post: the two side-by-side outputs go together")
+    if c_out is not None:
+        _need(c_out.shape == (cq.shape[0], rank) and k_out.shape == (cq.shape[0], rot_dim) and c_out.dtype == k_out.dtype == cq.dtype,
+              "latent_post: side-by-side outputs")
     T = cq.shape[0]
     _need(lat.dtype == torch.float32 and lat.shape == (T, q_rank + rank + rot_dim), "latent_post: input shape or dtype")
     _need(cq.shape == (T, q_rank) and cq.dtype in DT, "latent_post: query latent")
@@ -684,7 +689,7 @@ def latent_post(lat, q_gain, c_gain, cos, sin, cq, pool, tok_seq, tok_pos, block
     _need(tok_seq.dtype == torch.int32 and tok_pos.dtype == torch.int32, "latent_post: token tables are int32")
     lib().call("slb_latent_post", _p(lat), _p(q_gain), _p(c_gain), _p(cos), _p(sin), _p(cq), _p(pool), _p(tok_seq),
                _p(tok_pos), _p(block_table), stride, T, q_rank, rank, rot_dim, rotated, float(eps), DT[cq.dtype],
-               stream if stream is not None else current_stream())
+               _p(c_out), _p(k_out), stream if stream is not None else current_stream())
 
 
 def latent_attention_supported(rank: int, rot_dim: int) -> bool:
@@ -735,6 +740,33 @@ def latent_attention(q_lat, q_raw, pool, out, cos, sin, seq_start, past, counts,
     lib().call("slb_latent_attention", _p(q_lat), _p(q_raw), _p(pool), _p(out), _p(scratch), _p(cos), _p(sin),
                _p(seq_start), _p(past), _p(counts), _p(block_table), block_table.shape[1], n, int(max_count), T, heads,
                rank, rot_dim, plain_dim, rotated, int(window), float(scale), int(splits), DT[out.dtype],
+               stream if stream is not None else current_stream())
+
+
+def head_prompt_supported(plain_dim: int, rot_dim: int, value_dim: int, dtype: torch.dtype) -> bool:
+    """Whether whole prompts of these head sizes can run as per-head attention (``head_prompt_attention``)."""
+    if dtype != torch.bfloat16:
+        return False
+    fn = lib().dll.slb_head_prompt_supported
+    fn.argtypes, fn.restype = [ctypes.c_int] * 3, ctypes.c_int
+    return bool(fn(int(plain_dim), int(rot_dim), int(value_dim)))
+
+
+def head_prompt_attention(q, kv, k_rot, out, cos, sin, seq_start, counts, max_count: int, heads: int, plain_dim: int,
+                          rot_dim: int, value_dim: int, rotated: int, window: int, scale: float, stream=None) -> None:
+    """Causal attention of whole prompts (every sequence starts at position 0) with per-head keys and values, bfloat16.
+    q [T, heads, plain_dim + rot_dim] (rotated part turned as it is read); kv [T, heads * plain_dim + heads *
+    value_dim]: every head's unrotated key values, then every head's values; k_rot [T, rot_dim] turned already;
+    out [heads, T, value_dim]."""
+    _cuda(q, kv, k_rot, out, cos, sin, seq_start, counts)
+    T = q.shape[0]
+    _need(q.shape == (T, heads, plain_dim + rot_dim) and kv.shape == (T, heads * (plain_dim + value_dim))
+          and k_rot.shape == (T, rot_dim) and out.shape == (heads, T, value_dim), "head_prompt_attention: shapes")
+    _need(q.dtype == kv.dtype == k_rot.dtype == out.dtype == torch.bfloat16, "head_prompt_attention: bfloat16 only")
+    if rotated:
+        _need(cos is not None and cos.dtype == torch.float32 and cos.shape[1] == rotated // 2, "head_prompt_attention: rotation tables")
+    lib().call("slb_head_prompt_attention", _p(q), _p(kv), _p(k_rot), _p(out), _p(cos), _p(sin), _p(seq_start), _p(counts),
+               counts.numel(), int(max_count), T, heads, plain_dim, rot_dim, value_dim, rotated, int(window), float(scale),
                stream if stream is not None else current_stream())
 
 

@@ -16,7 +16,13 @@ q_plain . (W_uk c) = q_lat . c), the softmax-weighted sum runs over the latents,
 applied to that sum (value[n] = W_uv[n] sum_j p_j c_j). One kernel then serves prompts, single tokens and chunks
 alike, and a token costs ``kv_rank + rot_dim`` cache values per layer whatever the number of heads.
 
-Launches of a step: the stacked down-projections (float32 result), the gate projection, ``latent_post`` (both
+A bfloat16 step in which every sequence starts at position 0 (whole prompts of 64 tokens and more) takes another
+way to the same result: its keys are its own tokens, so one product forms every head's unrotated keys and values
+from the step's latents and ``head_prompt_attention`` runs ordinary per-head attention, which multiplies
+``plain_dim + rot_dim + value_dim`` values per head and pair of tokens instead of ``2 * kv_rank + rot_dim``. The cache
+is written the same way, and later portions and single tokens read it through the latent form.
+
+Launches of a step (latent form): the stacked down-projections (float32 result), the gate projection, ``latent_post`` (both
 norms, the key part's rotation, the cache write), the query up-projection, the per-head carry into the latent
 space (a batched library product), ``latent_attention`` (which turns the queries' rotated part as it loads them),
 the per-head value up-projection (batched library product), ``latent_gate``, the output projection.
@@ -31,6 +37,12 @@ from ..kernels import ops
 from .base import BuildContext, Normed, ParamDecl, Part, build_position, register_mixer
 from .linear import Linear
 from .spec import LatentAttentionSpec
+
+
+# From this many tokens of its longest sequence on, a bfloat16 step in which every sequence starts at position 0 (whole
+# prompts) forms each head's keys and values from its own tokens' latents and runs ordinary per-head attention: that
+# multiplies plain_dim + rot_dim + value_dim values per head and token pair instead of 2 * kv_rank + rot_dim.
+PER_HEAD_PROMPT_TOKENS = 64
 
 
 class LatentAttention(Part):
@@ -62,6 +74,7 @@ class LatentAttention(Part):
         self.gate = Linear(t["g.weight"], dt) if s.output_gate else None
         self.uq = Linear(t["uq.weight"], dt)
         self.o = Linear(t["o.weight"], dt)
+        self.ukv = Linear(torch.cat([t["uk.weight"], t["uv.weight"]], dim=0), dt)      # whole prompts: keys and values per head
         self.w_uk = t["uk.weight"].to(dt).view(s.heads, s.plain_dim, s.kv_rank).contiguous()
         self.w_uv_t = t["uv.weight"].to(dt).view(s.heads, s.value_dim, s.kv_rank).transpose(1, 2)   # [H, rank, value]
         self.q_gain, self.c_gain = t["dq_norm.weight"], t["dkv_norm.weight"]
@@ -86,9 +99,21 @@ class LatentAttention(Part):
         lat = self.down.forward(h, ws=ws, stream=b.stream, out_dtype=torch.float32)
         g = self.gate.forward(h, ws=ws, stream=b.stream) if self.gate is not None else None
         cq = ws.take((T, s.q_rank), dt)
+        per_head = (getattr(b, "fresh", False) and b.max_count >= PER_HEAD_PROMPT_TOKENS
+                    and ops.head_prompt_supported(dn, P, dv, dt))
+        c_out = ws.take((T, R), dt) if per_head else None
+        k_out = ws.take((T, P), dt) if per_head else None
         ops.latent_post(lat, self.q_gain, self.c_gain, cos, sin, cq, view.pool if view.writes else None, b.tok_seq,
-                        b.tok_pos, table, s.q_rank, R, P, rotated, s.norm_eps, b.stream)
+                        b.tok_pos, table, s.q_rank, R, P, rotated, s.norm_eps, b.stream, c_out, k_out)
         q = self.uq.forward(cq, ws=ws, stream=b.stream).view(T, H, dn + P)
+        if per_head:
+            kv = self.ukv.forward(c_out, ws=ws, stream=b.stream)
+            val = ws.take((H, T, dv), dt)
+            ops.head_prompt_attention(q, kv, k_out, val, cos, sin, b.seq_start, b.counts, b.max_count, H, dn, P, dv, rotated,
+                                      view.window, s.scale, b.stream)
+            self._gate_and_project(val, g, x, b, ws, T, H, dv, dt)
+            ws.release(mark)
+            return
         q_lat = ws.take((H, T, R), dt)
         torch.bmm(q[:, :, :dn].transpose(0, 1), self.w_uk, out=q_lat)
         o_lat = ws.take((H, T, R), dt)
@@ -101,13 +126,16 @@ class LatentAttention(Part):
                              H, R, P, dn, rotated, view.window, s.scale, splits, scratch, b.stream)
         val = ws.take((H, T, dv), dt)
         torch.bmm(o_lat, self.w_uv_t, out=val)
+        self._gate_and_project(val, g, x, b, ws, T, H, dv, dt)
+        ws.release(mark)
+
+    def _gate_and_project(self, val, g, x, b, ws, T, H, dv, dt):
         y = ws.take((T, H * dv), dt)
         if g is not None:
             ops.latent_gate(val, g, y, b.stream)
         else:
             y.view(T, H, dv).copy_(val.transpose(0, 1))
         self.o.forward(y, into=x, ws=ws, stream=b.stream, next_read=getattr(b, "next_read", None))
-        ws.release(mark)
 
 
 register_mixer("latent_attention", LatentAttention)

@@ -168,6 +168,43 @@ def test_attention_in_slices_is_the_same_attention(splits, dtype, R, P):
     torch.testing.assert_close(cut[0], one[0], rtol=1e-5, atol=1e-5) if dtype == "fp32" else None
 
 
+@pytest.mark.parametrize("H, dn, P, dv, R", [(3, 16, 16, 16, 40), (8, 64, 32, 64, 96), (2, 128, 64, 128, 72), (5, 24, 8, 48, 24)])
+def test_whole_prompts_with_per_head_keys_and_values(H, dn, P, dv, R):
+    """Every sequence starts at 0: keys and values per head formed from the latents, then per-head attention; loud keys
+    at the first token, at page borders and far back."""
+    o, dt = ops(), torch.bfloat16
+    counts = [1, 65, 300, 64]
+    loud = [(1, 64, 0), (1, 63, 62), (2, 299, 0), (2, 298, 63), (2, 297, 64), (2, 200, 128), (3, 63, 1)]
+    w_uk, w_uv, seqs = latent_case(H, dn, P, dv, R, [0] * 4, counts, seed=H + dn, loud=loud)
+    for s_ in seqs:
+        for k in s_:
+            s_[k] = s_[k].to(dt).double()
+    base, scale = 1000.0, 0.3
+    cos, sin = rot_tables(max(counts) + 1, base, P)
+    T = sum(counts)
+    q = torch.cat([s_["q"] for s_ in seqs]).reshape(T, H, dn + P)
+    c = torch.cat([s_["c"] for s_ in seqs])
+    kv = torch.cat([c @ w_uk.T, c @ w_uv.T], dim=-1).to(dt)
+    k_rot = torch.cat([plain.rotate_half_pairs(s_["k_rot"][:, None, :], torch.arange(len(s_["c"])), base, P)[:, 0] for s_ in seqs]).to(dt)
+    out = torch.empty(H, T, dv, dtype=dt, device=DEV)
+    starts = np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
+    assert o.head_prompt_supported(dn, P, dv, dt)
+    o.head_prompt_attention(q.to(dt).to(DEV).contiguous(), kv.to(DEV).contiguous(), k_rot.to(DEV).contiguous(), out, cos, sin,
+                            torch.from_numpy(starts).to(DEV), torch.tensor(counts, dtype=torch.int32, device=DEV), max(counts), H,
+                            dn, P, dv, P, 0, scale)
+    want, at = [], 0
+    for s_ in seqs:          # both sides see the same rounded keys and values
+        n = len(s_["c"])
+        pos = torch.arange(n)
+        mine = kv[at:at + n].double()
+        qq = torch.cat([s_["q"][..., :dn], plain.rotate_half_pairs(s_["q"][..., dn:], pos, base, P)], -1)
+        kk = torch.cat([mine[:, :H * dn].reshape(n, H, dn), k_rot[at:at + n].double()[:, None, :].expand(n, H, P)], -1)
+        want.append(plain.causal_softmax_attention(qq, kk, mine[:, H * dn:].reshape(n, H, dv), scale))
+        at += n
+    torch.testing.assert_close(out.cpu().double().transpose(0, 1), torch.cat(want), **TOL["bf16"])
+    assert float(torch.cat(want).abs().max()) > 0.5
+
+
 def test_the_two_bfloat16_attention_kernels_agree():
     """The tensor-core kernel and the general one on the same bfloat16 inputs: portions behind earlier tokens, single
     tokens and whole prompts in one step, more heads than a block takes."""
