@@ -512,7 +512,7 @@ __global__ void __launch_bounds__(128) latent_attn_mma_kernel(const LatentAttnAr
 // When every sequence of a step starts at position 0 its keys are the step's own tokens, and forming each head's
 // unrotated key and value from the latents (one product for all tokens) costs little beside an attention that then
 // multiplies d_n + d_r + d_v instead of r + d_r + r values per head and pair of tokens. Block: 64 query rows of one
-// (sequence, head) on four warps; the query fragments stay in registers (the rotated part is turned as it is loaded);
+// (sequence, head) on four warps; the queries stay in shared memory (the rotated part is turned as it is loaded);
 // 64 keys a step in shared memory: the head's unrotated key values and the shared rotated part side by side, and the
 // head's values; mma.sync m16n8k16, float32 sums, online softmax in registers.
 struct HeadPromptArgs {
@@ -529,13 +529,13 @@ struct HeadPromptArgs {
 };
 
 template <int KQ, int NV>       // at most KQ * 16 key values and NV * 16 value columns a head
-__global__ void __launch_bounds__(128) head_prompt_mma_kernel(const HeadPromptArgs a) {
+__global__ void __launch_bounds__(128, NV <= 4 ? 4 : (NV <= 8 ? 3 : 2)) head_prompt_mma_kernel(const HeadPromptArgs a, int nbuf) {
   pdl_enter();
   extern __shared__ __align__(16) unsigned char hp_raw[];
   const int DK = a.dn + a.P, ksd = DK + 8, vsd = a.dv + 8;
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(hp_raw);   // [64][ksd]
-  __nv_bfloat16* Ks = Qs + 64 * ksd;                              // two buffers of [64][ksd]
-  __nv_bfloat16* Vs = Ks + 128 * ksd;                             // two buffers of [64][vsd]
+  __nv_bfloat16* Ks = Qs + 64 * ksd;                              // nbuf buffers of [64][ksd]
+  __nv_bfloat16* Vs = Ks + nbuf * 64 * ksd;                       // nbuf buffers of [64][vsd]
   const int seq = blockIdx.y, h = blockIdx.z;
   const int count = a.counts[seq];
   const int n_tiles = (count + 63) / 64;
@@ -569,10 +569,7 @@ __global__ void __launch_bounds__(128) head_prompt_mma_kernel(const HeadPromptAr
   }
   __syncthreads();
   const int kq = DK / 16, nv = a.dv / 16;
-  uint32_t qf[KQ][4];
-#pragma unroll
-  for (int kb = 0; kb < KQ; ++kb)
-    if (kb < kq) ldmatrix_x4(qf[kb], smem_u32(Qs) + 2 * ((warp * 16 + (lane & 15)) * ksd + kb * 16 + ((lane >> 4) << 3)));
+  const uint32_t q_at = smem_u32(Qs) + 2 * ((warp * 16 + (lane & 15)) * ksd + ((lane >> 4) << 3));   // this lane's part of a query fragment
   int pos_r[2], lo_r[2];
 #pragma unroll
   for (int hh = 0; hh < 2; ++hh) {
@@ -608,13 +605,16 @@ __global__ void __launch_bounds__(128) head_prompt_mma_kernel(const HeadPromptAr
     cp_async_commit();
   };
 
-  load_keys(key_lo, 0);
+  // With two buffers the next 64 keys are on their way while these are multiplied; with one (chosen when that lets
+  // more blocks share an SM) other blocks' products hide the wait.
+  if (nbuf == 2) load_keys(key_lo, 0);
   int buf = 0;
-  for (int k0 = key_lo; k0 <= last_pos; k0 += 64, buf ^= 1) {
-    if (k0 + 64 <= last_pos) {        // the next 64 keys are on their way while these are multiplied
+  for (int k0 = key_lo; k0 <= last_pos; k0 += 64, buf = nbuf == 2 ? buf ^ 1 : 0) {
+    if (nbuf == 2 && k0 + 64 <= last_pos) {
       load_keys(k0 + 64, buf ^ 1);
       cp_async_wait<1>();
     } else {
+      if (nbuf == 1) load_keys(k0, 0);
       cp_async_wait<0>();
     }
     __syncthreads();
@@ -626,12 +626,14 @@ __global__ void __launch_bounds__(128) head_prompt_mma_kernel(const HeadPromptAr
 #pragma unroll
     for (int kb = 0; kb < KQ; ++kb) {
       if (kb < kq) {
+        uint32_t qf[4];          // fetched again every step: keeping all of them would cost the registers of a block more an SM
+        ldmatrix_x4(qf, q_at + 2 * kb * 16);
 #pragma unroll
         for (int jp = 0; jp < 4; ++jp) {
           uint32_t kf[4];
           ldmatrix_x4(kf, k_base + 2 * ((jp * 16 + (lane & 7) + ((lane >> 4) << 3)) * ksd + kb * 16 + (((lane >> 3) & 1) << 3)));
-          mma_bf16(s[2 * jp], qf[kb], kf[0], kf[1]);
-          mma_bf16(s[2 * jp + 1], qf[kb], kf[2], kf[3]);
+          mma_bf16(s[2 * jp], qf, kf[0], kf[1]);
+          mma_bf16(s[2 * jp + 1], qf, kf[2], kf[3]);
         }
       }
     }
@@ -930,7 +932,10 @@ extern "C" int slb_head_prompt_attention(const void* q, const void* kv, const vo
   a.q = (const __nv_bfloat16*)q; a.kv = (const __nv_bfloat16*)kv; a.k_rot = (const __nv_bfloat16*)k_rot;
   a.out = (__nv_bfloat16*)out; a.cos_t = cos_t; a.sin_t = sin_t; a.seq_start = seq_start; a.counts = counts;
   a.T = T; a.H = H; a.dn = dn; a.P = P; a.dv = dv; a.rot = rot; a.window = window; a.scale = scale;
-  const size_t smem = (size_t)(192 * (dn + P + 8) + 128 * (dv + 8)) * 2;
+  // two key buffers where four blocks still fit an SM's shared memory with them, else one
+  const size_t smem2 = (size_t)(192 * (dn + P + 8) + 128 * (dv + 8)) * 2, smem1 = (size_t)(128 * (dn + P + 8) + 64 * (dv + 8)) * 2;
+  const int nbuf = smem2 * 4 <= kLatMaxSmem ? 2 : 1;
+  const size_t smem = nbuf == 2 ? smem2 : smem1;
   const dim3 grid((max_count + 63) / 64, n_seqs, H), block(128);
   cudaStream_t s = (cudaStream_t)stream;
   const int kq = (dn + P) / 16, nv = dv / 16;
@@ -941,7 +946,7 @@ extern "C" int slb_head_prompt_attention(const void* q, const void* kv, const vo
       cudaFuncSetAttribute(head_prompt_mma_kernel<KQ, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kLatMaxSmem); \
       raised = true;                                                                                            \
     }                                                                                                           \
-    launch(head_prompt_mma_kernel<KQ, NV>, grid, block, smem, s, a);                                            \
+    launch(head_prompt_mma_kernel<KQ, NV>, grid, block, smem, s, a, nbuf);                                         \
   } while (0)
   if (kq <= 8) {
     if (nv <= 4) SLB_HP(8, 4); else if (nv <= 8) SLB_HP(8, 8); else SLB_HP(8, 16);
