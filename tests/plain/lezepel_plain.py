@@ -138,3 +138,14 @@ def forward(cfg, w, tokens, work=torch.float64, keep_stream=False):
         kept.append(x)
     logits = rms_norm(x, w["final.norm"], eps) @ w["head"].T
     return (logits, torch.stack(kept)) if keep_stream else logits
+
+
+def greedy_generate(cfg, w, prompt, n, work=torch.float64):
+    """The ``n`` tokens that always taking the largest logit gives after ``prompt`` (the whole sequence is run again
+    for every token: slow and plain)."""
+    seq, out = list(prompt), []
+    for _ in range(n):
+        tok = int(torch.argmax(forward(cfg, w, seq, work)[-1]))
+        out.append(tok)
+        seq.append(tok)
+    return out

@@ -97,3 +97,29 @@ def test_generate_command_end_to_end(tmp_path):
     want = plain.greedy_generate(cfg, w, prompts[0], 8, stop_ids={stop})
     assert out[0].split() == [str(t) for t in want] and out[1] == "-" * 40 and out[2] == out[0]
     assert "stop: stop_token" in r.stderr
+
+
+@pytest.mark.gpu
+def test_the_commands_serve_a_lezepel_folder_too(tmp_path):
+    """``random-model`` and ``generate`` with a Lezepel ``config.json``: the registry chooses the family, nothing in the
+    commands knows it."""
+    import tiny_lezepel
+    from plain import lezepel_plain
+    env = dict(os.environ, PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    cfg_path = tmp_path / "config.json"
+    cfg_path.write_text(json.dumps(tiny_lezepel.P))
+    folder = tmp_path / "model"
+    r = subprocess.run([sys.executable, "-m", "sleuth_b200", "random-model", str(cfg_path), str(folder), "--seed", "3",
+                        "--dtype", "fp32"], env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr
+    cfg, w = plain.read_model(folder)
+    assert cfg["architecture"] == "Lezepel" and "l1.mlp.router.b" in w and w["loop.step"].shape == (2, 72)
+    prompts = [[5, 17, 3, 250, 9], [300, 2], [77]]
+    text = "; ".join(",".join(map(str, p)) for p in prompts)
+    r = subprocess.run([sys.executable, "-m", "sleuth_b200", "generate", str(folder), "--prompt-ids", text, "--temperature", "0",
+                        "--max-new-tokens", "6", "--dtype", "fp32", "--max-seq-len", "128"],
+                       env=env, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stderr
+    lines = [ln for ln in r.stdout.splitlines() if ln.strip()]
+    assert [[int(t) for t in ln.split()] for ln in lines] == [lezepel_plain.greedy_generate(cfg, w, p, 6) for p in prompts]
+    assert any("LezepelConfig" in ln for ln in r.stderr.splitlines())
