@@ -425,11 +425,12 @@ __global__ void __launch_bounds__(128) moe_mma_kernel(const __nv_bfloat16* __res
 }
 
 // ---- few pairs (single-token steps): a warp per output, every weight row streamed once per pair that uses it ----
-// grid (pairs, column groups of 8): act[place[pair], j] = f(gate_e[j] . h[token]) * (up_e[j] . h[token]).
+// (act rows lie in the order of the pairs here: nothing needs the expert order, so a step of few pairs skips the layout.)
+// grid (pairs, column groups of 8): act[pair, j] = f(gate_e[j] . h[token]) * (up_e[j] . h[token]).
 template <typename T>
 __global__ void __launch_bounds__(256) moe_few_gate_up_kernel(const T* __restrict__ h, const T* __restrict__ w_gu,
-                                                              const int* __restrict__ choice, const int* __restrict__ place,
-                                                              T* __restrict__ act, int top, int dim, int ff, int relu) {
+                                                              const int* __restrict__ choice, T* __restrict__ act, int top,
+                                                              int dim, int ff, int relu) {
   pdl_enter();
   const int pair = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int j = blockIdx.y * 8 + warp;
@@ -470,40 +471,44 @@ __global__ void __launch_bounds__(256) moe_few_gate_up_kernel(const T* __restric
   u = warp_sum(u);
   if (lane == 0) {
     const float f = relu ? fmaxf(g, 0.f) : g / (1.0f + expf(-g));
-    act[(size_t)place[pair] * ff + j] = from_f32<T>(f * u);
+    act[(size_t)pair * ff + j] = from_f32<T>(f * u);
   }
 }
 
-// grid (pairs, column groups of 8): y[pair, n] = weight[pair] * (down_e[n] . act[place[pair]]).
+// grid (tokens, column groups of 8): x[t, n] += sum over the token's choices, in their order, of
+// weight[pair] * (down_e[n] . act[pair]).
 template <typename T>
 __global__ void __launch_bounds__(256) moe_few_down_kernel(const T* __restrict__ act, const T* __restrict__ w_down,
-                                                           const int* __restrict__ choice, const int* __restrict__ place,
-                                                           const float* __restrict__ weight, float* __restrict__ y, int dim,
-                                                           int ff) {
+                                                           const int* __restrict__ choice, const float* __restrict__ weight,
+                                                           float* __restrict__ x, int top, int dim, int ff) {
   pdl_enter();
-  const int pair = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n = blockIdx.y * 8 + warp;
   if (n >= dim) return;
-  const T* a = act + (size_t)place[pair] * ff;
-  const T* w = w_down + ((size_t)choice[pair] * dim + n) * ff;
-  float s = 0.f;
-  if constexpr (sizeof(T) == 2) {
-    if (ff % 8 == 0) {
-      for (int k = lane * 8; k < ff; k += 256) {
-        float af[8], wf[8];
-        unpack8(*reinterpret_cast<const Bf16x8*>(a + k), af);
-        unpack8(*reinterpret_cast<const Bf16x8*>(w + k), wf);
+  float total = 0.f;
+  for (int k = 0; k < top; ++k) {
+    const int pair = t * top + k;
+    const T* a = act + (size_t)pair * ff;
+    const T* w = w_down + ((size_t)choice[pair] * dim + n) * ff;
+    float s = 0.f;
+    if constexpr (sizeof(T) == 2) {
+      if (ff % 8 == 0) {
+        for (int i = lane * 8; i < ff; i += 256) {
+          float af[8], wf[8];
+          unpack8(*reinterpret_cast<const Bf16x8*>(a + i), af);
+          unpack8(*reinterpret_cast<const Bf16x8*>(w + i), wf);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) s = fmaf(af[i], wf[i], s);
+          for (int u = 0; u < 8; ++u) s = fmaf(af[u], wf[u], s);
+        }
+      } else {
+        for (int i = lane; i < ff; i += 32) s = fmaf(to_f32(a[i]), to_f32(w[i]), s);
       }
     } else {
-      for (int k = lane; k < ff; k += 32) s = fmaf(to_f32(a[k]), to_f32(w[k]), s);
+      for (int i = lane; i < ff; i += 32) s = fmaf(to_f32(a[i]), to_f32(w[i]), s);
     }
-  } else {
-    for (int k = lane; k < ff; k += 32) s = fmaf(to_f32(a[k]), to_f32(w[k]), s);
+    total = fmaf(weight[pair], warp_sum(s), total);
   }
-  s = warp_sum(s);
-  if (lane == 0) y[(size_t)pair * dim + n] = weight[pair] * s;
+  if (lane == 0) x[(size_t)t * dim + n] += total;
 }
 
 __global__ void moe_combine_kernel(float* __restrict__ x, const float* __restrict__ y, int top, int dim, size_t total) {
@@ -582,8 +587,8 @@ extern "C" int slb_moe_experts_tc(const void* h, const void* w_gu, const void* w
 // logits: float32 scratch [tokens, E], or null (then every token's block forms its own logits). tiles: int32
 // [1 + 3 * (tokens * top / 128 + min(tokens * top, E))] for the grouped tensor-memory product, or null.
 extern "C" int slb_moe_route(const void* h, const float* w_router, const float* bias, int* choice, float* weight,
-                             int* rank, int* counts, int* place, int* list, float* logits, int* tiles, int tokens, int dim,
-                             int E, int top, int dtype, void* stream) {
+                             int* rank, int* counts, int* place, int* list, float* logits, int* tiles, int layout,
+                             int tokens, int dim, int E, int top, int dtype, void* stream) {
   SLB_REQUIRE(tokens >= 0 && dim > 0 && E > 0 && top > 0 && top <= E, "moe_route: tokens=%d dim=%d experts=%d top=%d",
               tokens, dim, E, top);
   SLB_REQUIRE(E <= 4096, "moe_route: at most 4096 experts, got %d", E);
@@ -609,7 +614,7 @@ extern "C" int slb_moe_route(const void* h, const float* w_router, const float* 
     launch(moe_route_kernel<__nv_bfloat16>, grid, block, smem, s, (const __nv_bfloat16*)h, w_router, bias, given, choice, weight,
            tokens, dim, E, top);
   int rc = check_launch("moe_route");
-  if (rc) return rc;
+  if (rc || !layout) return rc;        // a step of few pairs needs no counts and no expert order
   const int pairs = tokens * top;
   launch(moe_group_kernel, dim3(1), dim3(pairs >= 1024 ? 1024 : 256), 2 * sizeof(int) * E, s, (const int*)choice, counts, place, list,
          pairs, E, tiles, 128);
@@ -617,7 +622,8 @@ extern "C" int slb_moe_route(const void* h, const float* w_router, const float* 
 }
 
 // act: [tokens * top, ff] in the run dtype; y: float32 [tokens * top, dim]; x: the float32 stream [tokens, dim].
-// choice and place (from slb_moe_route) serve steps of few pairs, which run a warp per output instead of tiles.
+// choice (from slb_moe_route) serves steps of few pairs, which run a warp per output instead of tiles and need neither
+// the counts nor the expert-ordered list (`place` is accepted for callers that have it and is not read).
 extern "C" int slb_moe_experts(const void* h, const void* w_gu, const void* w_down, const int* counts, const int* list,
                                const int* choice, const int* place, const float* weight, void* act, float* y, float* x,
                                int tokens, int dim, int ff, int E, int top, int relu, int dtype, void* stream) {
@@ -633,17 +639,18 @@ extern "C" int slb_moe_experts(const void* h, const void* w_gu, const void* w_do
   const dim3 block(256);
   const dim3 g1((unsigned)tiles, (ff + 31) / 32), g2((unsigned)tiles, (dim + kMoeCols - 1) / kMoeCols);
   const bool aligned = ((uintptr_t)h | (uintptr_t)w_gu | (uintptr_t)w_down | (uintptr_t)act) % 16 == 0;
-  if (pairs <= kMoeFewPairs && choice != nullptr && place != nullptr && (dtype == kF32 || aligned)) {
-    const dim3 f1((unsigned)pairs, (ff + 7) / 8), f2((unsigned)pairs, (dim + 7) / 8);
+  if (pairs <= kMoeFewPairs && choice != nullptr && (dtype == kF32 || aligned)) {
+    const dim3 f1((unsigned)pairs, (ff + 7) / 8), f2((unsigned)tokens, (dim + 7) / 8);
     if (dtype == kF32) {
-      launch(moe_few_gate_up_kernel<float>, f1, block, 0, s, (const float*)h, (const float*)w_gu, choice, place, (float*)act, top, dim, ff, relu);
-      launch(moe_few_down_kernel<float>, f2, block, 0, s, (const float*)act, (const float*)w_down, choice, place, weight, y, dim, ff);
+      launch(moe_few_gate_up_kernel<float>, f1, block, 0, s, (const float*)h, (const float*)w_gu, choice, (float*)act, top, dim, ff, relu);
+      launch(moe_few_down_kernel<float>, f2, block, 0, s, (const float*)act, (const float*)w_down, choice, weight, x, top, dim, ff);
     } else {
-      launch(moe_few_gate_up_kernel<__nv_bfloat16>, f1, block, 0, s, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w_gu, choice, place,
+      launch(moe_few_gate_up_kernel<__nv_bfloat16>, f1, block, 0, s, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w_gu, choice,
              (__nv_bfloat16*)act, top, dim, ff, relu);
-      launch(moe_few_down_kernel<__nv_bfloat16>, f2, block, 0, s, (const __nv_bfloat16*)act, (const __nv_bfloat16*)w_down, choice, place,
-             weight, y, dim, ff);
+      launch(moe_few_down_kernel<__nv_bfloat16>, f2, block, 0, s, (const __nv_bfloat16*)act, (const __nv_bfloat16*)w_down, choice,
+             weight, x, top, dim, ff);
     }
+    return check_launch("moe_experts");          // the down kernel has added into the stream already
   } else if (dtype == kBF16 && dim % 8 == 0 && ff % 8 == 0 && aligned) {
     const long long tiles64 = pairs / kMmaRows + (pairs < E ? pairs : E);
     launch(moe_mma_kernel<true>, dim3((unsigned)tiles64, (ff + 63) / 64), dim3(128), 0, s, (const __nv_bfloat16*)h,

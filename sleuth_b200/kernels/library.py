@@ -156,7 +156,7 @@ _SIGNATURES = {
     "slb_head_prompt_attention": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P],
     "slb_latent_attention": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, I, P],
     "slb_latent_gate": [P, P, P, I, I, I, I, P],
-    "slb_moe_route": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, P],
+    "slb_moe_route": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, P],
     "slb_moe_experts_tc": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, P, P],
     "slb_moe_experts": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P],
 }

@@ -786,12 +786,17 @@ def moe_tile_words(tokens: int, top: int, experts: int) -> int:
     return 1 + 3 * (pairs // 128 + min(pairs, experts))
 
 
+MOE_FEW_PAIRS = 64      # up to this many (token, choice) pairs ``moe_experts`` runs a warp per output (csrc/moe.cu: kMoeFewPairs)
+
+
 def moe_route(h, w_router, bias, choice, weight, rank, counts, place, order, top: int, stream=None, logits=None,
-              tiles=None) -> None:
+              tiles=None, layout: bool = True) -> None:
     """Router logits in float32, the ``top`` largest per token, softmax over those; then the (token, choice) pairs are
     laid out expert by expert: counts [experts], place [T * top] (a pair's row in that order), order [T * top] (the
     pair at each row). choice, rank int32 [T * top]; weight float32 [T * top]. ``logits``: float32 scratch
-    [T, experts]; with it, steps of many tokens form their logits 32 tokens at a time (the same sums, k ascending)."""
+    [T, experts]; with it, steps of many tokens form their logits 32 tokens at a time (the same sums, k ascending).
+    ``layout=False`` leaves counts, place and order unwritten: ``moe_experts`` with ``choice`` does not read them for
+    steps of at most ``MOE_FEW_PAIRS`` pairs."""
     _cuda(h, w_router, bias, choice, weight, rank, counts, place, order, logits, tiles)
     T, d = h.shape
     E = w_router.shape[0]
@@ -804,7 +809,7 @@ def moe_route(h, w_router, bias, choice, weight, rank, counts, place, order, top
     _need(logits is None or (logits.dtype == torch.float32 and logits.numel() >= T * E), "moe_route: scratch for the logits")
     _need(tiles is None or (tiles.dtype == torch.int32 and tiles.numel() >= moe_tile_words(T, top, E)), "moe_route: row-tile table")
     lib().call("slb_moe_route", _p(h), _p(w_router), _p(bias), _p(choice), _p(weight), _p(rank), _p(counts), _p(place),
-               _p(order), _p(logits), _p(tiles), T, d, E, int(top), DT[h.dtype], stream if stream is not None else current_stream())
+               _p(order), _p(logits), _p(tiles), 1 if layout else 0, T, d, E, int(top), DT[h.dtype], stream if stream is not None else current_stream())
 
 
 def moe_experts(h, w_gate_up, w_down, counts, order, weight, act, y, x, top: int, activation: str = "silu",

@@ -71,7 +71,8 @@ class RoutedExperts(Part):
         grouped = (dt == torch.bfloat16 and s.activation == "silu" and pairs >= TC_PAIRS and s.hidden % 8 == 0
                    and s.intermediate % 8 == 0)
         tiles = ws.take((ops.moe_tile_words(T, s.top, s.experts),), torch.int32) if grouped else None
-        ops.moe_route(h, self.w_router, self.bias, choice, weight, rank, counts, place, order, s.top, b.stream, logits, tiles)
+        ops.moe_route(h, self.w_router, self.bias, choice, weight, rank, counts, place, order, s.top, b.stream, logits, tiles,
+                      layout=pairs > ops.MOE_FEW_PAIRS)
         if grouped:
             xs = ws.take((pairs, s.hidden), dt)
             ops.moe_experts_tc(h, self.w_gate_up, self.w_down, order, place, weight, tiles, xs, act, y, x, s.top, b.stream)

@@ -272,6 +272,14 @@ def test_router_and_experts(T, d, ff, E, top, dtype):
     y = torch.empty(pairs, d, dtype=torch.float32, device=DEV)
     x = x0.clone().to(DEV)
     o.moe_experts(h.to(DEV), gu, dn, counts, order, weight, act, y, x, top, "silu", choice=choice, place=place)
+    if pairs <= o.MOE_FEW_PAIRS:      # a step of few pairs needs no layout at all
+        junk = [torch.full((max(pairs, E),), -7, dtype=torch.int32, device=DEV) for _ in range(3)]
+        o.moe_route(h.to(DEV), w["router"].to(DEV), w["router.b"].to(DEV), choice, weight, rank, junk[0], junk[1], junk[2], top,
+                    layout=False)
+        x4 = x0.clone().to(DEV)
+        o.moe_experts(h.to(DEV), gu, dn, junk[0], junk[2], weight, act, y, x4, top, "silu", choice=choice)
+        torch.testing.assert_close(x4, x, rtol=0, atol=0)
+        assert all(int((j != -7).sum()) == 0 for j in junk)
     x2 = x0.clone().to(DEV)          # and through the tiles whatever the number of pairs
     o.moe_experts(h.to(DEV), gu, dn, counts, order, weight, act, y, x2, top, "silu")
     torch.testing.assert_close(x2, x, **TOL[dtype])
