@@ -76,6 +76,31 @@ __global__ void __launch_bounds__(256) moe_logits_kernel(const T* __restrict__ h
   }
 }
 
+// Router logits for few tokens: a warp per (token, expert), so that a single token's step still has experts * 32 lanes
+// fetching the router's rows at once (one block walking them alone waits for memory a hundred times in a row).
+template <typename T>
+__global__ void __launch_bounds__(256) moe_logits_few_kernel(const T* __restrict__ h, const float* __restrict__ wr,
+                                                             const float* __restrict__ bias, float* __restrict__ z, int tokens,
+                                                             int dim, int E) {
+  pdl_enter();
+  const int id = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (id >= tokens * E) return;
+  const int t = id / E, e = id - t * E;
+  const T* row = h + (size_t)t * dim;
+  const float* w = wr + (size_t)e * dim;
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  int i = lane;
+  for (; i + 96 < dim; i += 128) {
+    s0 = fmaf(to_f32(row[i]), w[i], s0);
+    s1 = fmaf(to_f32(row[i + 32]), w[i + 32], s1);
+    s2 = fmaf(to_f32(row[i + 64]), w[i + 64], s2);
+    s3 = fmaf(to_f32(row[i + 96]), w[i + 96], s3);
+  }
+  for (; i < dim; i += 32) s0 = fmaf(to_f32(row[i]), w[i], s0);
+  const float sum = warp_sum((s0 + s1) + (s2 + s3));
+  if (lane == 0) z[id] = sum + (bias ? bias[e] : 0.f);
+}
+
 // One block of eight warps per token. Without given logits a warp forms the logits of every eighth expert (the lanes
 // share the row, four partial sums each, joined in a fixed order); warp 0 then picks the `top` largest.
 template <typename T>
@@ -600,7 +625,14 @@ extern "C" int slb_moe_route(const void* h, const float* w_router, const float* 
   const dim3 grid(tokens), block(256);
   // from a few tokens on the logits are formed 32 tokens and 16 experts at a time, each weight read once a block
   const float* given = nullptr;
-  if (logits != nullptr && tokens >= 16) {
+  if (logits != nullptr && tokens < 16) {         // few tokens: a warp per (token, expert)
+    const dim3 lg((tokens * E + 7) / 8), lb(256);
+    if (dtype == kF32) launch(moe_logits_few_kernel<float>, lg, lb, 0, s, (const float*)h, w_router, bias, logits, tokens, dim, E);
+    else launch(moe_logits_few_kernel<__nv_bfloat16>, lg, lb, 0, s, (const __nv_bfloat16*)h, w_router, bias, logits, tokens, dim, E);
+    int rc0 = check_launch("moe_logits");
+    if (rc0) return rc0;
+    given = logits;
+  } else if (logits != nullptr) {
     const dim3 lg((tokens + 31) / 32, (E + 15) / 16), lb(256);
     if (dtype == kF32) launch(moe_logits_kernel<float>, lg, lb, 0, s, (const float*)h, w_router, bias, logits, tokens, dim, E);
     else launch(moe_logits_kernel<__nv_bfloat16>, lg, lb, 0, s, (const __nv_bfloat16*)h, w_router, bias, logits, tokens, dim, E);

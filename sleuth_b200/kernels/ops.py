@@ -705,13 +705,13 @@ def latent_attention_general_only(on: bool) -> None:
 
 def latent_splits(n_seqs: int, heads: int, max_count: int, max_len: int, sms: int | None = None) -> int:
     """Into how many slices the keys of a step are cut: none while the step's own blocks fill the SMs, else as many
-    as it takes to give every SM about two blocks, each slice at least two pages long."""
+    as it takes to give every SM about two blocks, a slice being at least one page long."""
     sms = sms or sm_count()
     hb = min(heads, 64)
     blocks = n_seqs * -(-max_count // (64 // hb)) * -(-heads // hb)
     if blocks >= sms or max_len <= 128:
         return 1
-    return int(max(1, min(2 * sms // max(blocks, 1), max_len // 128, 64)))
+    return int(max(1, min(2 * sms // max(blocks, 1), max_len // 64, 64)))
 
 
 def latent_scratch_floats(tokens: int, heads: int, rank: int, splits: int) -> int:
