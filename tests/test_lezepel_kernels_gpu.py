@@ -47,7 +47,7 @@ def paged(rows_per_seq, width, dtype, seed):
 
 
 @pytest.mark.parametrize("dtype", ["fp32", "bf16"])
-@pytest.mark.parametrize("q_rank, R, P, rot", [(20, 40, 8, 8), (80, 96, 32, 32), (7, 9, 6, 4), (300, 520, 64, 64)])
+@pytest.mark.parametrize("q_rank, R, P, rot", [(20, 40, 8, 8), (64, 112, 16, 16), (7, 9, 6, 4), (300, 520, 64, 64)])
 def test_norms_rotation_and_cache_write(q_rank, R, P, rot, dtype):
     g = torch.Generator().manual_seed(q_rank)
     pasts, counts = [70, 0, 63], [3, 5, 2]
@@ -134,7 +134,7 @@ def run_latent_attention(H, dn, P, dv, R, pasts, counts, dtype, seed, loud=(), s
 
 
 @pytest.mark.parametrize("dtype", ["fp32", "bf16"])
-@pytest.mark.parametrize("H, dn, P, dv, R", [(3, 16, 8, 24, 40), (8, 64, 32, 64, 96), (1, 8, 4, 8, 7), (40, 8, 4, 8, 28),
+@pytest.mark.parametrize("H, dn, P, dv, R", [(3, 16, 8, 24, 40), (8, 48, 16, 64, 112), (1, 8, 4, 8, 7), (40, 8, 4, 8, 28),
                                              (5, 16, 64, 16, 520), (70, 8, 16, 8, 32), (5, 16, 64, 16, 512), (2, 8, 16, 8, 272)])
 def test_attention_over_the_latent_cache_prompts(H, dn, P, dv, R, dtype):
     got, want = run_latent_attention(H, dn, P, dv, R, pasts=[0, 0, 0, 0], counts=[1, 65, 130, 17], dtype=dtype, seed=H)
@@ -168,7 +168,7 @@ def test_attention_in_slices_is_the_same_attention(splits, dtype, R, P):
     torch.testing.assert_close(cut[0], one[0], rtol=1e-5, atol=1e-5) if dtype == "fp32" else None
 
 
-@pytest.mark.parametrize("H, dn, P, dv, R", [(3, 16, 16, 16, 40), (8, 64, 32, 64, 96), (2, 128, 64, 128, 72), (5, 24, 8, 48, 24)])
+@pytest.mark.parametrize("H, dn, P, dv, R", [(3, 16, 16, 16, 40), (8, 48, 16, 64, 80), (2, 128, 64, 128, 72), (5, 24, 8, 48, 24)])
 def test_whole_prompts_with_per_head_keys_and_values(H, dn, P, dv, R):
     """Every sequence starts at 0: keys and values per head formed from the latents, then per-head attention; loud keys
     at the first token, at page borders and far back."""
@@ -242,7 +242,7 @@ def expert_weights(E, d, ff, seed, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["fp32", "bf16"])
-@pytest.mark.parametrize("T, d, ff, E, top", [(1, 72, 36, 5, 2), (77, 72, 20, 6, 1), (300, 256, 96, 16, 4), (40, 64, 16, 4, 4),
+@pytest.mark.parametrize("T, d, ff, E, top", [(1, 72, 36, 5, 2), (77, 72, 20, 6, 1), (300, 192, 88, 12, 3), (40, 64, 16, 4, 4),
                                               (9, 50, 33, 70, 3), (700, 128, 200, 7, 3), (3, 64, 136, 5, 2)])
 def test_router_and_experts(T, d, ff, E, top, dtype):
     o, dt = ops(), DT[dtype]

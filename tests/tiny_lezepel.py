@@ -39,10 +39,10 @@ R = {"architecture": "Lezepel", "vocab": 203, "width": 64, "norm": {"eps": 1e-5}
      "layers": [layer(mixer(1, 16, 16, 8, 24, 24), dense(48)), layer(mixer(40, 8, 4, 8, 32, 28, base=100.0), moe(4, 4, 16))]}
 
 # sizes that send prompts of 128 tokens and more through the tensor-memory products and single tokens through the
-# weight-streaming kernel: every inner size a multiple of 64
-_MS = mixer(4, 64, 32, 64, 128, 128)
-S = {"architecture": "Lezepel", "vocab": 640, "width": 256, "norm": {"eps": 1e-6}, "embedding": {"scale": 4.0},
-     "layers": [layer(_MS, dense(512)), layer(_MS, moe(8, 2, 128)), layer(_MS, moe(8, 2, 128))],
+# weight-streaming kernel, whole prompts through the per-head attention kernel: every inner size a multiple of 16
+_MS = mixer(4, 64, 32, 48, 128, 128)
+S = {"architecture": "Lezepel", "vocab": 640, "width": 320, "norm": {"eps": 1e-6}, "embedding": {"scale": 4.0},
+     "layers": [layer(_MS, dense(640)), layer(_MS, moe(8, 2, 128)), layer(_MS, moe(8, 2, 128))],
      "loop": {"start": 1, "stop": 2, "times": 2}}
 
 CONFIGS = {"P": P, "Q": Q, "R": R, "S": S}
