@@ -5,7 +5,9 @@ Each layer application has one cache *entry*. A part asks for what its entry nee
 * ``KVRequest(kv_heads, head_dim, window)``: keys and values of every position (or of the last
   ``window`` positions). Entries with equal requests form a *group*; a group owns one tensor
   ``[entries, 2, pages, kv_heads, 64, head_dim]`` (index 1: 0 = keys, 1 = values), so a page number
-  means the same place in every entry of the group and one block table serves them all.
+  means the same place in every entry of the group and one block table serves them all. With values of another
+  width than the keys (``value_dim``) an entry is one flat run instead: all key pages ``[pages, kv_heads, 64,
+  head_dim]``, then all value pages ``[pages, kv_heads, 64, value_dim]``.
 * ``LatentRequest(width, window)``: one row of ``width`` values per position, which all heads of the layer read
   both as key and as value (attention through a low-rank latent keeps the normed latent and the shared rotated
   key part there instead of per-head keys and values). Entries with equal requests form a group with one tensor
@@ -36,6 +38,7 @@ class KVRequest:
     kv_heads: int
     head_dim: int
     window: int = 0
+    value_dim: int = 0          # width of a value row when it is not head_dim (0 = head_dim)
 
 
 @dataclass(frozen=True)
@@ -54,7 +57,7 @@ class StateRequest:
 class KVView:
     """What an attention part gets for its entry in one step."""
     k_pool: torch.Tensor        # [pages, kv_heads, 64, head_dim]
-    v_pool: torch.Tensor
+    v_pool: torch.Tensor        # [pages, kv_heads, 64, value_dim or head_dim]
     group: int                  # which block table of the step's batch applies
     window: int
     writes: bool                # this application owns the entry and stores its keys and values
@@ -117,11 +120,16 @@ class PagedCache:
                 raise TypeError(f"cache entry {e}: unknown request {r!r}")
         self.group_requests = keys
         self.book = CacheBook([k.window for k in keys], self.n_pages, self.max_slots, self.stride)
-        self.pools = [torch.zeros((len(m), 2, self.n_pages, k.kv_heads, PAGE_TOKENS, k.head_dim) if isinstance(k, KVRequest)
-                                  else (len(m), self.n_pages, PAGE_TOKENS, k.width), dtype=dtype, device=self.device)
-                      for k, m in zip(keys, members)]
+        self.pools = [torch.zeros(self._pool_shape(k, len(m)), dtype=dtype, device=self.device) for k, m in zip(keys, members)]
         self.states = {e: torch.zeros((self.max_slots, *r.shape), dtype=r.dtype, device=self.device)
                        for e, r in enumerate(self.requests) if isinstance(r, StateRequest)}
+
+    def _pool_shape(self, k, entries: int) -> tuple:
+        if isinstance(k, LatentRequest):
+            return (entries, self.n_pages, PAGE_TOKENS, k.width)
+        if k.value_dim in (0, k.head_dim):
+            return (entries, 2, self.n_pages, k.kv_heads, PAGE_TOKENS, k.head_dim)
+        return (entries, self.n_pages * k.kv_heads * PAGE_TOKENS * (k.head_dim + k.value_dim))
 
     @property
     def n_groups(self) -> int:
@@ -131,7 +139,12 @@ class PagedCache:
         r = self.requests[entry]
         if isinstance(r, KVRequest):
             g, i = self.entry_group[entry], self.entry_index[entry]
-            return KVView(self.pools[g][i, 0], self.pools[g][i, 1], g, r.window, writes)
+            if r.value_dim in (0, r.head_dim):
+                return KVView(self.pools[g][i, 0], self.pools[g][i, 1], g, r.window, writes)
+            rows = self.n_pages * r.kv_heads * PAGE_TOKENS
+            flat = self.pools[g][i]
+            return KVView(flat[:rows * r.head_dim].view(self.n_pages, r.kv_heads, PAGE_TOKENS, r.head_dim),
+                          flat[rows * r.head_dim:].view(self.n_pages, r.kv_heads, PAGE_TOKENS, r.value_dim), g, r.window, writes)
         if isinstance(r, LatentRequest):
             g, i = self.entry_group[entry], self.entry_index[entry]
             return LatentView(self.pools[g][i], g, r.window, writes)

@@ -32,6 +32,8 @@ struct AttnArgs {
   int table_stride;
   int tokens, heads, kv_heads, head_dim, window;
   float scale;
+  const float* sinks;   // [H] or null: a learned score per head that joins the softmax denominator and has no value
+  int value_dim;        // width of a value row and of a head's output (head_dim is the width of queries and keys)
 };
 
 template <typename T> struct RowDot;
@@ -85,7 +87,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_generic_kernel(AttnArgs 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long item = blockIdx.x;
   const int t = (int)(item / a.heads), h = (int)(item - (long long)t * a.heads);
-  const int hd = a.head_dim;
+  const int hd = a.head_dim, vd = a.value_dim;
   const int kh = h / (a.heads / a.kv_heads);
   const int pos = a.tok_pos[t];
   const int* table = a.block_table + (size_t)a.tok_seq[t] * a.table_stride;
@@ -123,11 +125,11 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_generic_kernel(AttnArgs 
     for (int jj = first; jj <= last; ++jj) {
       const float pj = __shfl_sync(0xffffffffu, p, jj);
       const int rj = __shfl_sync(0xffffffffu, row, jj);
-      const T* vrow = vpool + (size_t)rj * hd;
+      const T* vrow = vpool + (size_t)rj * vd;
 #pragma unroll
       for (int i = 0; i < PER_LANE; ++i) {
         const int c = lane + 32 * i;
-        if (c < hd) acc[i] = fmaf(pj, to_f32(vrow[c]), acc[i]);
+        if (c < vd) acc[i] = fmaf(pj, to_f32(vrow[c]), acc[i]);
       }
     }
     m = m_new;
@@ -138,15 +140,18 @@ __global__ void __launch_bounds__(kAttnWarps * 32) attn_generic_kernel(AttnArgs 
   for (int i = 0; i < PER_LANE; ++i) part_acc[warp][lane + 32 * i] = acc[i];
   if (lane == 0) { part_m[warp] = m; part_l[warp] = l; }
   __syncthreads();
-  float top = -INFINITY;
+  // a sink counts once in the denominator, unscaled, after the warps' sums
+  const float sink = a.sinks ? a.sinks[h] : -INFINITY;
+  float top = sink;
 #pragma unroll
   for (int w = 0; w < kAttnWarps; ++w) top = fmaxf(top, part_m[w]);
   float total = 0.0f;
 #pragma unroll
   for (int w = 0; w < kAttnWarps; ++w) total += part_l[w] * expf(part_m[w] - top);
-  T* o = (T*)a.out + ((size_t)t * a.heads + h) * hd;
+  if (a.sinks) total += expf(sink - top);
+  T* o = (T*)a.out + ((size_t)t * a.heads + h) * vd;
   const float inv = 1.0f / total;
-  for (int c = threadIdx.x; c < hd; c += kAttnWarps * 32) {
+  for (int c = threadIdx.x; c < vd; c += kAttnWarps * 32) {
     float v = 0.0f;
 #pragma unroll
     for (int w = 0; w < kAttnWarps; ++w) v += part_acc[w][c] * expf(part_m[w] - top);
@@ -159,7 +164,7 @@ static int launch_attn_generic(const AttnArgs& a, cudaStream_t s) {
   const long long items = (long long)a.tokens * a.heads;
   const long long blocks = items;
   SLB_REQUIRE(blocks < (1ll << 31), "attention: too many rows (%lld)", items);
-  const int per_lane = (a.head_dim + 31) / 32;
+  const int per_lane = (a.value_dim + 31) / 32;
   const int threads = kAttnWarps * 32;
   switch (per_lane) {
     case 1: launch(attn_generic_kernel<T, 1>, dim3((int)blocks), dim3(threads), 0, s, a); break;
@@ -178,18 +183,20 @@ using namespace slb;
 extern "C" int slb_attention_generic(const void* q, const void* k_pool, const void* v_pool, void* out,
                                      const int* tok_seq, const int* tok_pos, const int* block_table,
                                      int table_stride, int tokens, int heads, int kv_heads, int head_dim, int window,
-                                     float scale, int dtype, void* stream) {
+                                     float scale, const float* sinks, int value_dim, int dtype, void* stream) {
   SLB_REQUIRE(tokens >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0,
               "attention: tokens=%d heads=%d kv_heads=%d", tokens, heads, kv_heads);
   SLB_REQUIRE(head_dim > 0 && head_dim <= 256 && head_dim % 2 == 0,
               "attention: head_dim %d is not supported (even, at most 256)", head_dim);
   SLB_REQUIRE(window >= 0 && table_stride > 0, "attention: window=%d table_stride=%d", window, table_stride);
+  if (value_dim == 0) value_dim = head_dim;
+  SLB_REQUIRE(value_dim > 0 && value_dim <= 256, "attention: value size %d is not supported (at most 256)", value_dim);
   if (tokens == 0) return 0;
   AttnArgs a;
   a.q = q; a.k_pool = k_pool; a.v_pool = v_pool; a.out = out;
   a.tok_seq = tok_seq; a.tok_pos = tok_pos; a.block_table = block_table; a.table_stride = table_stride;
   a.tokens = tokens; a.heads = heads; a.kv_heads = kv_heads; a.head_dim = head_dim; a.window = window;
-  a.scale = scale;
+  a.scale = scale; a.sinks = sinks; a.value_dim = value_dim;
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == kF32) return launch_attn_generic<float>(a, s);
   if (dtype == kBF16) return launch_attn_generic<__nv_bfloat16>(a, s);

@@ -244,6 +244,25 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
   return scratch[32];
 }
 
+// The gated activations of the feed-forwards: f(g, u) for a gate value g and an up value u, float32.
+//   silu:           g * sigmoid(g) * u
+//   relu:           max(g, 0) * u
+//   clamped swish:  g' = min(g, limit), u' = clamp(u, -limit, limit);  g' * sigmoid(alpha * g') * (u' + 1)
+enum GateKind : int { kGateSilu = 0, kGateRelu = 1, kGateClampedSwish = 2 };
+struct GateAct {
+  int kind;
+  float limit, alpha;      // read by the clamped swish only
+};
+__device__ __forceinline__ float gated(const GateAct& a, float g, float u) {
+  if (a.kind == kGateRelu) return fmaxf(g, 0.0f) * u;
+  if (a.kind == kGateClampedSwish) {
+    g = fminf(g, a.limit);
+    u = fminf(fmaxf(u, -a.limit), a.limit);
+    return (g / (1.0f + expf(-a.alpha * g))) * (u + 1.0f);
+  }
+  return (g / (1.0f + expf(-g))) * u;
+}
+
 // 8 bfloat16 values in one 16-byte register group.
 struct alignas(16) Bf16x8 {
   __nv_bfloat162 v[4];

@@ -136,9 +136,10 @@ __global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __nv_
   }
 }
 
-// act[t, j] = f(gu[t, j]) * gu[t, inter + j] with f = relu; float32 arithmetic. (The SiLU form has kernels of its own above.)
+// act[t, j] = f(gu[t, j], gu[t, inter + j]) for the gated activations of common.cuh; float32 arithmetic. (The SiLU form
+// has kernels of its own above.)
 template <typename T>
-__global__ void relu_gate_kernel(const T* __restrict__ gu, T* __restrict__ act, int inter, size_t total) {
+__global__ void gate_kernel(const T* __restrict__ gu, T* __restrict__ act, int inter, size_t total, GateAct f) {
   pdl_enter();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   const size_t step = (size_t)gridDim.x * blockDim.x;
@@ -146,7 +147,48 @@ __global__ void relu_gate_kernel(const T* __restrict__ gu, T* __restrict__ act, 
     const size_t t = i / inter, j = i - t * inter;
     const float g = to_f32(gu[t * 2 * inter + j]);
     const float u = to_f32(gu[t * 2 * inter + inter + j]);
-    act[i] = from_f32<T>(fmaxf(g, 0.0f) * u);
+    act[i] = from_f32<T>(gated(f, g, u));
+  }
+}
+
+// Layer norm with a gain and no bias: out[r, :] = (x[row(r), :] - mean) / sqrt(var + eps) * w, var = the mean of the
+// squared deviations (formed from the deviations, in a second pass over the row, which sits in shared memory), float32
+// arithmetic, one rounding at the store. out may be x itself (float32): a block reads its whole row before it writes.
+template <typename TO>
+__global__ void layernorm_kernel(const float* __restrict__ x, const float* __restrict__ w, TO* __restrict__ out,
+                                 const int* __restrict__ rows, int dim, float eps) {
+  pdl_enter();
+  extern __shared__ float row[];        // [dim]
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  const float* xr = x + (size_t)(rows ? rows[r] : r) * dim;
+  float sum = 0.0f;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+    const float v = xr[i];
+    row[i] = v;
+    sum += v;
+  }
+  const float mean = block_sum(sum, scratch) / (float)dim;
+  float ss = 0.0f;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+    const float d = row[i] - mean;
+    ss = fmaf(d, d, ss);
+  }
+  const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)dim + eps);
+  TO* o = out + (size_t)r * dim;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) o[i] = from_f32<TO>(((row[i] - mean) * inv) * w[i]);
+}
+
+// v <- cap * tanh(v / cap), in place, float32.
+__global__ void softcap_kernel(float* __restrict__ v, long long row_stride, int cols, size_t total, float cap) {
+  pdl_enter();
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t step = (size_t)gridDim.x * blockDim.x;
+  const float inv = 1.0f / cap;
+  for (; i < total; i += step) {
+    const size_t r = i / cols, c = i - r * cols;
+    float* p = v + r * row_stride + c;
+    *p = cap * tanhf(*p * inv);
   }
 }
 
@@ -260,23 +302,54 @@ extern "C" int slb_swiglu(const void* gu, void* act, int dtype, int tokens, int 
   return check_launch("swiglu");
 }
 
-// kind: 0 = silu (the kernels of slb_swiglu), 1 = relu.
-extern "C" int slb_gated_act(const void* gu, void* act, int dtype, int tokens, int inter, int kind, void* stream) {
-  if (kind == 0) return slb_swiglu(gu, act, dtype, tokens, inter, stream);
-  SLB_REQUIRE(kind == 1, "gated_act: unknown activation %d", kind);
+// kind: 0 = silu (the kernels of slb_swiglu), 1 = relu, 2 = clamped swish with `limit` and `alpha` (common.cuh).
+extern "C" int slb_gated_act(const void* gu, void* act, int dtype, int tokens, int inter, int kind, float limit, float alpha,
+                             void* stream) {
+  if (kind == kGateSilu) return slb_swiglu(gu, act, dtype, tokens, inter, stream);
+  SLB_REQUIRE(kind == kGateRelu || kind == kGateClampedSwish, "gated_act: unknown activation %d", kind);
+  SLB_REQUIRE(kind != kGateClampedSwish || limit > 0.0f, "gated_act: the clamp limit must be positive, got %g", (double)limit);
   SLB_REQUIRE(tokens >= 0 && inter > 0, "gated_act: tokens=%d inter=%d", tokens, inter);
   if (tokens == 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
   const size_t total = (size_t)tokens * inter;
   size_t blocks = (total + 255) / 256;
   if (blocks > (size_t)sm_count() * 16) blocks = (size_t)sm_count() * 16;
+  const GateAct f{kind, limit, alpha};
   if (dtype == kF32)
-    launch(relu_gate_kernel<float>, dim3((int)blocks), dim3(256), 0, s, (const float*)gu, (float*)act, inter, total);
+    launch(gate_kernel<float>, dim3((int)blocks), dim3(256), 0, s, (const float*)gu, (float*)act, inter, total, f);
   else if (dtype == kBF16)
-    launch(relu_gate_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(256), 0, s, (const __nv_bfloat16*)gu, (__nv_bfloat16*)act, inter, total);
+    launch(gate_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(256), 0, s, (const __nv_bfloat16*)gu, (__nv_bfloat16*)act, inter, total, f);
   else
     return fail(1, "gated_act: unknown dtype %d", dtype);
   return check_launch("gated_act");
+}
+
+extern "C" int slb_layernorm(const float* x, const float* w, void* out, int out_dtype, const int* rows, int n_rows,
+                             int dim, float eps, void* stream) {
+  SLB_REQUIRE(n_rows >= 0 && dim > 0 && dim <= 12288 && eps > 0.0f, "layernorm: rows=%d dim=%d (at most 12288) eps=%g", n_rows, dim,
+              (double)eps);
+  if (n_rows == 0) return 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int threads = norm_threads(dim);
+  const size_t smem = (size_t)dim * sizeof(float);
+  if (out_dtype == kF32)
+    launch(layernorm_kernel<float>, dim3(n_rows), dim3(threads), smem, s, x, w, (float*)out, rows, dim, eps);
+  else if (out_dtype == kBF16)
+    launch(layernorm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), smem, s, x, w, (__nv_bfloat16*)out, rows, dim, eps);
+  else
+    return fail(1, "layernorm: unknown dtype %d", out_dtype);
+  return check_launch("layernorm");
+}
+
+extern "C" int slb_softcap(float* v, long long row_stride, int rows, int cols, float cap, void* stream) {
+  SLB_REQUIRE(rows >= 0 && cols > 0 && row_stride >= cols && cap > 0.0f, "softcap: rows=%d cols=%d stride=%lld cap=%g", rows, cols,
+              row_stride, (double)cap);
+  if (rows == 0) return 0;
+  const size_t total = (size_t)rows * cols;
+  size_t blocks = (total + 255) / 256;
+  if (blocks > (size_t)sm_count() * 16) blocks = (size_t)sm_count() * 16;
+  launch(softcap_kernel, dim3((int)blocks), dim3(256), 0, (cudaStream_t)stream, v, row_stride, cols, total, cap);
+  return check_launch("softcap");
 }
 
 extern "C" int slb_stream_inject(float* x, const float* again, const float* row, int tokens, int dim, void* stream) {

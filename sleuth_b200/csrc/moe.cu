@@ -6,10 +6,11 @@
 // routed experts can therefore be recorded once and replayed.
 //
 //   moe_route_kernel     logits = W_r h + b in float32, the `top` largest (lowest index first among equals), weights
-//                        = softmax over the chosen logits
+//                        = softmax over the chosen logits; or (RouteRule) sigmoid scores, the choice limited to the
+//                        best groups of neighbouring experts, weights = the chosen scores over their sum, scaled
 //   moe_group_kernel     counts the pairs of each expert; place[pair] = where the pair's row lies in the
 //                        expert-ordered list, list[place] = pair
-//   moe_gate_up_kernel   act[place, j] = f(gate_e[j] . h) * (up_e[j] . h), f = silu or relu
+//   moe_gate_up_kernel   act[place, j] = f(gate_e[j] . h, up_e[j] . h), f one of the gated activations of common.cuh
 //   moe_down_kernel      y[pair, :] = weight[pair] * (down_e act[place])   (float32)
 //   moe_combine_kernel   x[t, :] += sum over the token's choices of y, in the order of the choices
 // In bfloat16 with inner sizes that are multiples of 8 the two products run on the tensor cores (moe_mma_kernel);
@@ -101,15 +102,26 @@ __global__ void __launch_bounds__(256) moe_logits_few_kernel(const T* __restrict
   if (lane == 0) z[id] = sum + (bias ? bias[e] : 0.f);
 }
 
+// How the router turns logits into a choice and weights.
+//   scoring 0: the `top` largest logits; weights = softmax over those logits alone.
+//   scoring 1: scores = sigmoid(logit). The experts form `groups` equal groups of neighbours; a group's score is the sum
+//              of its two largest scores (of its one score, if it has one expert); only experts of the `keep` best
+//              groups can be chosen. The `top` largest scores among them; weights = score / (sum of the chosen scores
+//              + 1e-20) * scale.
+struct RouteRule {
+  int scoring, groups, keep;
+  float scale;
+};
+
 // One block of eight warps per token. Without given logits a warp forms the logits of every eighth expert (the lanes
 // share the row, four partial sums each, joined in a fixed order); warp 0 then picks the `top` largest.
 template <typename T>
 __global__ void __launch_bounds__(256) moe_route_kernel(const T* __restrict__ h, const float* __restrict__ wr,
                                                         const float* __restrict__ bias, const float* __restrict__ given,
                                                         int* __restrict__ choice, float* __restrict__ weight, int tokens,
-                                                        int dim, int E, int top) {
+                                                        int dim, int E, int top, RouteRule rule) {
   pdl_enter();
-  extern __shared__ float z[];         // [E]
+  extern __shared__ float z[];         // [E], then [groups] group scores and [groups] flags when groups limit the choice
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
   const T* row = h + (size_t)t * dim;
@@ -132,7 +144,46 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const T* __restrict__ h,
     }
   }
   __syncthreads();
+  if (rule.scoring == 1) {
+    for (int e = threadIdx.x; e < E; e += blockDim.x) z[e] = 1.0f / (1.0f + expf(-z[e]));
+    __syncthreads();
+  }
   if (warp != 0) return;
+  if (rule.scoring == 1 && rule.groups > 1 && rule.keep < rule.groups) {
+    float* gscore = z + E;
+    int* open = reinterpret_cast<int*>(gscore + rule.groups);
+    const int size = E / rule.groups;
+    for (int g = lane; g < rule.groups; g += 32) {
+      float a = -INFINITY, b = -INFINITY;          // the two largest of the group
+      for (int e = g * size; e < (g + 1) * size; ++e) {
+        const float v = z[e];
+        if (v > a) { b = a; a = v; } else if (v > b) { b = v; }
+      }
+      gscore[g] = size > 1 ? a + b : a;
+      open[g] = 0;
+    }
+    __syncwarp();
+    for (int k = 0; k < rule.keep; ++k) {
+      float best = -INFINITY;
+      int best_g = rule.groups;
+      for (int g = lane; g < rule.groups; g += 32) {
+        const float v = gscore[g];
+        if (v > best) { best = v; best_g = g; }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int og = __shfl_xor_sync(0xffffffffu, best_g, o);
+        if (ov > best || (ov == best && og < best_g)) { best = ov; best_g = og; }
+      }
+      best_g = min(best_g, rule.groups - 1);
+      if (lane == 0) { open[best_g] = 1; gscore[best_g] = -INFINITY; }
+      __syncwarp();
+    }
+    for (int e = lane; e < E; e += 32)
+      if (!open[e / size]) z[e] = -INFINITY;
+    __syncwarp();
+  }
   float first = 0.f, mass = 0.f;
   for (int k = 0; k < top; ++k) {
     float best = -INFINITY;
@@ -149,7 +200,7 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const T* __restrict__ h,
     }
     best_e = min(best_e, E - 1);                 // only logits that are not numbers get here
     if (k == 0) first = best;
-    const float p = expf(best - first);
+    const float p = rule.scoring == 1 ? best : expf(best - first);
     mass += p;
     if (lane == 0) {
       choice[(size_t)t * top + k] = best_e;
@@ -158,7 +209,11 @@ __global__ void __launch_bounds__(256) moe_route_kernel(const T* __restrict__ h,
     }
     __syncwarp();
   }
-  for (int k = lane; k < top; k += 32) weight[(size_t)t * top + k] /= mass;
+  if (rule.scoring == 1) {
+    for (int k = lane; k < top; k += 32) weight[(size_t)t * top + k] = weight[(size_t)t * top + k] / (mass + 1e-20f) * rule.scale;
+  } else {
+    for (int k = lane; k < top; k += 32) weight[(size_t)t * top + k] /= mass;
+  }
 }
 
 // One block lays the pairs out expert by expert: counts[e], then place[pair] = first row of the pair's expert + the
@@ -272,7 +327,7 @@ __device__ __forceinline__ void moe_tile_product(ARow a_row, BRow b_row, int row
 template <typename T>
 __global__ void __launch_bounds__(256) moe_gate_up_kernel(const T* __restrict__ h, const T* __restrict__ w_gu,
                                                           const int* __restrict__ counts, const int* __restrict__ list,
-                                                          T* __restrict__ act, int E, int top, int dim, int ff, int relu) {
+                                                          T* __restrict__ act, int E, int top, int dim, int ff, GateAct gate) {
   pdl_enter();
   __shared__ float As[kMoeK * (kMoeTile + 1)];
   __shared__ float Bs[kMoeK * (kMoeCols + 1)];
@@ -302,8 +357,7 @@ __global__ void __launch_bounds__(256) moe_gate_up_kernel(const T* __restrict__ 
     const int r = i / 32, j = i % 32;
     if (r >= rows || j >= nj) continue;
     const float g = Cs[r * 65 + j], u = Cs[r * 65 + 32 + j];
-    const float f = relu ? fmaxf(g, 0.f) : g / (1.0f + expf(-g));
-    act[(size_t)(row0 + r) * ff + j0 + j] = from_f32<T>(f * u);
+    act[(size_t)(row0 + r) * ff + j0 + j] = from_f32<T>(gated(gate, g, u));
   }
 }
 
@@ -350,7 +404,7 @@ template <bool GATED>
 __global__ void __launch_bounds__(128) moe_mma_kernel(const __nv_bfloat16* __restrict__ a_rows, const __nv_bfloat16* __restrict__ w,
                                                       const int* __restrict__ counts, const int* __restrict__ list,
                                                       const float* __restrict__ weight, __nv_bfloat16* __restrict__ act,
-                                                      float* __restrict__ y, int E, int top, int K, int N, int relu) {
+                                                      float* __restrict__ y, int E, int top, int K, int N, GateAct gate) {
   pdl_enter();
   __shared__ __align__(16) __nv_bfloat16 As[2][kMmaRows * kMmaPad];
   __shared__ __align__(16) __nv_bfloat16 Bs[2][kMmaCols * kMmaPad];
@@ -429,8 +483,7 @@ __global__ void __launch_bounds__(128) moe_mma_kernel(const __nv_bfloat16* __res
           const int c = j * 8 + 2 * t4 + e;
           if (c >= ncols) continue;
           const float gv = acc[j][2 * half + e], uv = acc[j + 8][2 * half + e];
-          const float f = relu ? fmaxf(gv, 0.f) : gv / (1.0f + expf(-gv));
-          dst[c] = __float2bfloat16_rn(f * uv);
+          dst[c] = __float2bfloat16_rn(gated(gate, gv, uv));
         }
       }
     } else {
@@ -455,7 +508,7 @@ __global__ void __launch_bounds__(128) moe_mma_kernel(const __nv_bfloat16* __res
 template <typename T>
 __global__ void __launch_bounds__(256) moe_few_gate_up_kernel(const T* __restrict__ h, const T* __restrict__ w_gu,
                                                               const int* __restrict__ choice, T* __restrict__ act, int top,
-                                                              int dim, int ff, int relu) {
+                                                              int dim, int ff, GateAct gate) {
   pdl_enter();
   const int pair = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int j = blockIdx.y * 8 + warp;
@@ -495,8 +548,7 @@ __global__ void __launch_bounds__(256) moe_few_gate_up_kernel(const T* __restric
   g = warp_sum(g);
   u = warp_sum(u);
   if (lane == 0) {
-    const float f = relu ? fmaxf(g, 0.f) : g / (1.0f + expf(-g));
-    act[(size_t)pair * ff + j] = from_f32<T>(f * u);
+    act[(size_t)pair * ff + j] = from_f32<T>(gated(gate, g, u));
   }
 }
 
@@ -613,15 +665,23 @@ extern "C" int slb_moe_experts_tc(const void* h, const void* w_gu, const void* w
 // [1 + 3 * (tokens * top / 128 + min(tokens * top, E))] for the grouped tensor-memory product, or null.
 extern "C" int slb_moe_route(const void* h, const float* w_router, const float* bias, int* choice, float* weight,
                              int* rank, int* counts, int* place, int* list, float* logits, int* tiles, int layout,
-                             int tokens, int dim, int E, int top, int dtype, void* stream) {
+                             int tokens, int dim, int E, int top, int scoring, int groups, int keep, float route_scale,
+                             int dtype, void* stream) {
   SLB_REQUIRE(tokens >= 0 && dim > 0 && E > 0 && top > 0 && top <= E, "moe_route: tokens=%d dim=%d experts=%d top=%d",
               tokens, dim, E, top);
   SLB_REQUIRE(E <= 4096, "moe_route: at most 4096 experts, got %d", E);
   SLB_REQUIRE(dtype == kF32 || dtype == kBF16, "moe_route: unknown dtype %d", dtype);
+  SLB_REQUIRE(scoring == 0 || scoring == 1, "moe_route: unknown scoring %d", scoring);
+  if (groups <= 0) groups = 1;
+  if (keep <= 0 || keep > groups) keep = groups;
+  SLB_REQUIRE(E % groups == 0, "moe_route: %d experts do not form %d equal groups", E, groups);
+  SLB_REQUIRE(scoring == 1 || groups == 1, "moe_route: groups of experts go with the sigmoid scoring");
+  SLB_REQUIRE((long long)keep * (E / groups) >= top, "moe_route: %d groups of %d experts cannot give %d choices", keep, E / groups, top);
   if (tokens == 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
   (void)rank;      // kept in the signature: callers hand over a table that older versions filled
-  const size_t smem = (size_t)E * sizeof(float);
+  const RouteRule rule{scoring, groups, keep, route_scale};
+  const size_t smem = (size_t)(E + 2 * groups) * sizeof(float);
   const dim3 grid(tokens), block(256);
   // from a few tokens on the logits are formed 32 tokens and 16 experts at a time, each weight read once a block
   const float* given = nullptr;
@@ -641,10 +701,10 @@ extern "C" int slb_moe_route(const void* h, const float* w_router, const float* 
     given = logits;
   }
   if (dtype == kF32)
-    launch(moe_route_kernel<float>, grid, block, smem, s, (const float*)h, w_router, bias, given, choice, weight, tokens, dim, E, top);
+    launch(moe_route_kernel<float>, grid, block, smem, s, (const float*)h, w_router, bias, given, choice, weight, tokens, dim, E, top, rule);
   else
     launch(moe_route_kernel<__nv_bfloat16>, grid, block, smem, s, (const __nv_bfloat16*)h, w_router, bias, given, choice, weight,
-           tokens, dim, E, top);
+           tokens, dim, E, top, rule);
   int rc = check_launch("moe_route");
   if (rc || !layout) return rc;        // a step of few pairs needs no counts and no expert order
   const int pairs = tokens * top;
@@ -658,12 +718,15 @@ extern "C" int slb_moe_route(const void* h, const float* w_router, const float* 
 // the counts nor the expert-ordered list (`place` is accepted for callers that have it and is not read).
 extern "C" int slb_moe_experts(const void* h, const void* w_gu, const void* w_down, const int* counts, const int* list,
                                const int* choice, const int* place, const float* weight, void* act, float* y, float* x,
-                               int tokens, int dim, int ff, int E, int top, int relu, int dtype, void* stream) {
+                               int tokens, int dim, int ff, int E, int top, int act_kind, float act_limit, float act_alpha,
+                               int dtype, void* stream) {
   SLB_REQUIRE(tokens >= 0 && dim > 0 && ff > 0 && E > 0 && top > 0, "moe_experts: tokens=%d dim=%d ff=%d experts=%d top=%d",
               tokens, dim, ff, E, top);
   SLB_REQUIRE(dtype == kF32 || dtype == kBF16, "moe_experts: unknown dtype %d", dtype);
+  SLB_REQUIRE(act_kind >= kGateSilu && act_kind <= kGateClampedSwish, "moe_experts: unknown activation %d", act_kind);
   if (tokens == 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
+  const GateAct gate{act_kind, act_limit, act_alpha};
   const long long pairs = (long long)tokens * top;
   // every expert with a pair has at most pairs/tile + 1 tiles more than full ones: an upper bound the host knows
   const long long tiles = pairs / kMoeTile + (pairs < E ? pairs : E);
@@ -674,11 +737,11 @@ extern "C" int slb_moe_experts(const void* h, const void* w_gu, const void* w_do
   if (pairs <= kMoeFewPairs && choice != nullptr && (dtype == kF32 || aligned)) {
     const dim3 f1((unsigned)pairs, (ff + 7) / 8), f2((unsigned)tokens, (dim + 7) / 8);
     if (dtype == kF32) {
-      launch(moe_few_gate_up_kernel<float>, f1, block, 0, s, (const float*)h, (const float*)w_gu, choice, (float*)act, top, dim, ff, relu);
+      launch(moe_few_gate_up_kernel<float>, f1, block, 0, s, (const float*)h, (const float*)w_gu, choice, (float*)act, top, dim, ff, gate);
       launch(moe_few_down_kernel<float>, f2, block, 0, s, (const float*)act, (const float*)w_down, choice, weight, x, top, dim, ff);
     } else {
       launch(moe_few_gate_up_kernel<__nv_bfloat16>, f1, block, 0, s, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w_gu, choice,
-             (__nv_bfloat16*)act, top, dim, ff, relu);
+             (__nv_bfloat16*)act, top, dim, ff, gate);
       launch(moe_few_down_kernel<__nv_bfloat16>, f2, block, 0, s, (const __nv_bfloat16*)act, (const __nv_bfloat16*)w_down, choice,
              weight, x, top, dim, ff);
     }
@@ -686,16 +749,16 @@ extern "C" int slb_moe_experts(const void* h, const void* w_gu, const void* w_do
   } else if (dtype == kBF16 && dim % 8 == 0 && ff % 8 == 0 && aligned) {
     const long long tiles64 = pairs / kMmaRows + (pairs < E ? pairs : E);
     launch(moe_mma_kernel<true>, dim3((unsigned)tiles64, (ff + 63) / 64), dim3(128), 0, s, (const __nv_bfloat16*)h,
-           (const __nv_bfloat16*)w_gu, counts, list, weight, (__nv_bfloat16*)act, (float*)nullptr, E, top, dim, ff, relu);
+           (const __nv_bfloat16*)w_gu, counts, list, weight, (__nv_bfloat16*)act, (float*)nullptr, E, top, dim, ff, gate);
     launch(moe_mma_kernel<false>, dim3((unsigned)tiles64, (dim + kMmaCols - 1) / kMmaCols), dim3(128), 0, s,
            (const __nv_bfloat16*)act, (const __nv_bfloat16*)w_down, counts, list, weight, (__nv_bfloat16*)nullptr, y, E, top, ff,
-           dim, relu);
+           dim, gate);
   } else if (dtype == kF32) {
-    launch(moe_gate_up_kernel<float>, g1, block, 0, s, (const float*)h, (const float*)w_gu, counts, list, (float*)act, E, top, dim, ff, relu);
+    launch(moe_gate_up_kernel<float>, g1, block, 0, s, (const float*)h, (const float*)w_gu, counts, list, (float*)act, E, top, dim, ff, gate);
     launch(moe_down_kernel<float>, g2, block, 0, s, (const float*)act, (const float*)w_down, counts, list, weight, y, E, dim, ff);
   } else {
     launch(moe_gate_up_kernel<__nv_bfloat16>, g1, block, 0, s, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w_gu, counts, list,
-           (__nv_bfloat16*)act, E, top, dim, ff, relu);
+           (__nv_bfloat16*)act, E, top, dim, ff, gate);
     launch(moe_down_kernel<__nv_bfloat16>, g2, block, 0, s, (const __nv_bfloat16*)act, (const __nv_bfloat16*)w_down, counts, list,
            weight, y, E, dim, ff);
   }

@@ -217,6 +217,118 @@ static int launch_qkv_post(const QkvPostArgs& a, cudaStream_t s) {
   return check_launch("qkv_post");
 }
 
+
+// The general form after separate q, k and v projections of any sizes: q [H * dk], k [G * dk], v [G * dv] side by side
+// in one float32 row per token. RMS norm of q and k either per head (gains [dk]) or over the whole projection at once
+// (all heads of q together, all heads of k together, before they are split; gains [H * dk] and [G * dk]), then the
+// rotation of the first rot_dim channels of each head, pairing channel i with i + rot_dim/2 (halves) or channel 2i with
+// 2i + 1 (neighbours): (a, b) -> (a cos - b sin, b cos + a sin) with the angle of pair i from the tables
+// [positions, rot_dim / 2]. Values are stored as they are. One block per token; float32 between the load and the one
+// rounding at the store; the sums of squares are formed head by head by one warp each and joined in head order, so a
+// token's result depends on nothing but its own row.
+struct QkvSpanArgs {
+  const float* qkv;         // [tokens, H * dk + G * dk + G * dv]
+  const float* q_gain;      // null: no norm
+  const float* k_gain;
+  const float* cos_table;   // [positions, rot / 2] or null
+  const float* sin_table;
+  void* q_out;              // [tokens, H, dk]
+  void* k_pool;             // [pages, G, 64, dk] or null
+  void* v_pool;             // [pages, G, 64, dv]
+  const int* tok_seq;
+  const int* tok_pos;
+  const int* block_table;
+  int table_stride;
+  int tokens, heads, kv_heads, key_dim, value_dim, rot_dim;
+  int neighbours;           // 1: pairs (2i, 2i + 1); 0: pairs (i, i + rot / 2)
+  int whole;                // 1: one norm over the whole projection; 0: one per head
+  float eps;
+};
+
+constexpr int kSpanMaxHeads = 512;     // q heads + kv heads
+
+template <typename T>
+__global__ void __launch_bounds__(256) qkv_post_span_kernel(QkvSpanArgs a) {
+  pdl_enter();
+  __shared__ float head_ss[kSpanMaxHeads];
+  __shared__ float inv_q, inv_k;
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int H = a.heads, G = a.kv_heads, dk = a.key_dim, dv = a.value_dim;
+  const size_t row_len = (size_t)(H + G) * dk + (size_t)G * dv;
+  const float* row = a.qkv + (size_t)t * row_len;
+  const bool normed = a.q_gain != nullptr;
+  if (normed) {
+    for (int hh = warp; hh < H + G; hh += 8) {
+      const float* src = row + (size_t)hh * dk;
+      float ss = 0.0f;
+      for (int c = lane; c < dk; c += 32) ss = fmaf(src[c], src[c], ss);
+      ss = warp_sum(ss);
+      if (lane == 0) head_ss[hh] = ss;
+    }
+    __syncthreads();
+    if (a.whole && threadIdx.x == 0) {
+      float sq = 0.0f, sk = 0.0f;
+      for (int hh = 0; hh < H; ++hh) sq += head_ss[hh];
+      for (int hh = H; hh < H + G; ++hh) sk += head_ss[hh];
+      inv_q = 1.0f / sqrtf(sq / (float)(H * dk) + a.eps);
+      inv_k = 1.0f / sqrtf(sk / (float)(G * dk) + a.eps);
+    }
+    __syncthreads();
+  }
+  const int pos = a.tok_pos[t];
+  const int half_rot = a.cos_table ? a.rot_dim >> 1 : 0;
+  const float* cs = a.cos_table ? a.cos_table + (size_t)pos * half_rot : nullptr;
+  const float* sn = a.cos_table ? a.sin_table + (size_t)pos * half_rot : nullptr;
+  T* kdst = nullptr;
+  T* vdst = nullptr;
+  if (a.k_pool != nullptr) {
+    const int page = a.block_table[(size_t)a.tok_seq[t] * a.table_stride + pos / kPageTokens];
+    const size_t slot = (size_t)page * G * kPageTokens + (pos % kPageTokens);      // + head * 64, in rows
+    kdst = (T*)a.k_pool + slot * dk;
+    vdst = (T*)a.v_pool + slot * dv;
+  }
+  const int pairs_per_head = dk >> 1;
+  for (int item = threadIdx.x; item < (H + G) * pairs_per_head; item += blockDim.x) {
+    const int hh = item / pairs_per_head, pi = item - hh * pairs_per_head;
+    const bool is_q = hh < H;
+    if (!is_q && kdst == nullptr) continue;
+    int c0, c1;
+    const bool turns = pi < half_rot;
+    if (turns) {
+      c0 = a.neighbours ? 2 * pi : pi;
+      c1 = a.neighbours ? 2 * pi + 1 : pi + half_rot;
+    } else {
+      c0 = 2 * half_rot + 2 * (pi - half_rot);
+      c1 = c0 + 1;
+    }
+    const float* src = row + (size_t)hh * dk;
+    float x0 = src[c0], x1 = src[c1];
+    if (normed) {
+      const float inv = a.whole ? (is_q ? inv_q : inv_k) : 1.0f / sqrtf(head_ss[hh] / (float)dk + a.eps);
+      const float* gain = is_q ? a.q_gain : a.k_gain;
+      const int g0 = a.whole ? (is_q ? hh : hh - H) * dk : 0;
+      x0 = (x0 * inv) * gain[g0 + c0];
+      x1 = (x1 * inv) * gain[g0 + c1];
+    }
+    if (turns) {
+      const float co = cs[pi], si = sn[pi];
+      const float y0 = x0 * co - x1 * si, y1 = x1 * co + x0 * si;
+      x0 = y0;
+      x1 = y1;
+    }
+    T* dst = is_q ? (T*)a.q_out + ((size_t)t * H + hh) * dk : kdst + (size_t)(hh - H) * kPageTokens * dk;
+    dst[c0] = from_f32<T>(x0);
+    dst[c1] = from_f32<T>(x1);
+  }
+  if (vdst != nullptr) {
+    const float* src = row + (size_t)(H + G) * dk;
+    for (int i = threadIdx.x; i < G * dv; i += blockDim.x) {
+      const int g = i / dv, c = i - g * dv;
+      vdst[(size_t)g * kPageTokens * dv + c] = from_f32<T>(src[i]);
+    }
+  }
+}
+
 }  // namespace slb
 
 using namespace slb;
@@ -247,4 +359,32 @@ extern "C" int slb_qkv_post(const void* qkv, const float* bias, const float* q_g
   if (dtype == kF32) return launch_qkv_post<float>(a, s);
   if (dtype == kBF16) return launch_qkv_post<__nv_bfloat16>(a, s);
   return fail(1, "qkv_post: unknown dtype %d", dtype);
+}
+
+extern "C" int slb_qkv_post_span(const float* qkv, const float* q_gain, const float* k_gain, const float* cos_table,
+                                 const float* sin_table, void* q_out, void* k_pool, void* v_pool, const int* tok_seq,
+                                 const int* tok_pos, const int* block_table, int table_stride, int tokens, int heads,
+                                 int kv_heads, int key_dim, int value_dim, int rot_dim, int neighbours, int whole, float eps,
+                                 int dtype, void* stream) {
+  SLB_REQUIRE(tokens >= 0 && heads > 0 && kv_heads > 0 && heads + kv_heads <= kSpanMaxHeads,
+              "qkv_post_span: tokens=%d heads=%d kv_heads=%d (at most %d heads together)", tokens, heads, kv_heads, kSpanMaxHeads);
+  SLB_REQUIRE(key_dim > 0 && key_dim % 2 == 0 && value_dim > 0, "qkv_post_span: key size %d must be even, value size %d positive",
+              key_dim, value_dim);
+  SLB_REQUIRE(rot_dim >= 0 && rot_dim <= key_dim && rot_dim % 2 == 0, "qkv_post_span: rot_dim=%d for key size %d", rot_dim, key_dim);
+  SLB_REQUIRE((q_gain == nullptr) == (k_gain == nullptr), "qkv_post_span: q and k gains go together");
+  SLB_REQUIRE(rot_dim == 0 || (cos_table && sin_table), "qkv_post_span: a rotation needs its tables");
+  SLB_REQUIRE(k_pool == nullptr || (v_pool && block_table && table_stride > 0), "qkv_post_span: a cache write needs both pools and a block table");
+  if (tokens == 0) return 0;
+  QkvSpanArgs a;
+  a.qkv = qkv; a.q_gain = q_gain; a.k_gain = k_gain;
+  a.cos_table = rot_dim > 0 ? cos_table : nullptr; a.sin_table = sin_table;
+  a.q_out = q_out; a.k_pool = k_pool; a.v_pool = v_pool;
+  a.tok_seq = tok_seq; a.tok_pos = tok_pos; a.block_table = block_table; a.table_stride = table_stride;
+  a.tokens = tokens; a.heads = heads; a.kv_heads = kv_heads; a.key_dim = key_dim; a.value_dim = value_dim; a.rot_dim = rot_dim;
+  a.neighbours = neighbours ? 1 : 0; a.whole = whole ? 1 : 0; a.eps = eps;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == kF32) launch(qkv_post_span_kernel<float>, dim3(tokens), dim3(256), 0, s, a);
+  else if (dtype == kBF16) launch(qkv_post_span_kernel<__nv_bfloat16>, dim3(tokens), dim3(256), 0, s, a);
+  else return fail(1, "qkv_post_span: unknown dtype %d", dtype);
+  return check_launch("qkv_post_span");
 }

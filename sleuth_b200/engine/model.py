@@ -54,13 +54,13 @@ class Model:
 
     # ---- weights ----
     def _end_names(self, which: str) -> dict[str, str]:
-        """Checkpoint names of the tensors an end part declares: ``weight`` (and the head's ``norm.weight``) from the
-        spec's own fields, anything else from the spec's ``names``."""
+        """Checkpoint names of the tensors an end part declares: ``weight`` (and ``norm.weight``, where the part has a
+        norm) from the spec's own fields, anything else from the spec's ``names``."""
         spec = getattr(self.spec, which)
         part = getattr(self, which)
         given = dict(getattr(spec, "names", {}) or {})
         given.setdefault("weight", spec.name)
-        if which == "head":
+        if getattr(spec, "norm_name", None):
             given.setdefault("norm.weight", spec.norm_name)
         out = {}
         for local in part.declare():
@@ -194,12 +194,16 @@ class Model:
         parts = [self.embedding, self.head]
         for layer in self.layers:
             parts.extend(getattr(layer, "children", {}).values())
-        for part in parts:
+        from ..parts.base import Part
+        while parts:
+            part = parts.pop()
             for v in vars(part).values():
                 if isinstance(v, torch.Tensor):
                     yield v
                 elif isinstance(getattr(v, "weight", None), torch.Tensor):
                     yield v.weight
+                elif isinstance(v, Part) and not isinstance(v, type(part)):
+                    parts.append(v)       # a part inside a part (a shared expert inside the routed experts)
 
 
 def declare_model(spec: ModelSpec) -> dict[str, ParamDecl]:

@@ -136,7 +136,7 @@ _SIGNATURES = {
     "slb_add": [P, P, I, L, P],
     "slb_swiglu": [P, P, I, I, I, P],
     "slb_qkv_post": [P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, P],
-    "slb_attention_generic": [P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, P],
+    "slb_attention_generic": [P, P, P, P, P, P, P, I, I, I, I, I, I, F, P, I, I, P],
     "slb_attention_prefill": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, P],
     "slb_attention_tc": [P, P, P, P, P, P, P, P, I, I, I, L, L, I, I, I, I, F, P, I, I, P],
     "slb_attention_decode": [P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, P, L, P, L, P, I, P, P, P, P, P, F, P, L, P],
@@ -150,15 +150,18 @@ _SIGNATURES = {
     "slb_penalize": [P, L, I, I, P, P, I, F, P, P, I, P],
     "slb_argmax": [P, L, I, I, P, P, L, P],
     "slb_sample": [P, L, I, I, F, I, F, F, P, P, P],
-    "slb_gated_act": [P, P, I, I, I, I, P],
+    "slb_gated_act": [P, P, I, I, I, I, F, F, P],
+    "slb_layernorm": [P, P, P, I, P, I, I, F, P],
+    "slb_softcap": [P, L, I, I, F, P],
+    "slb_qkv_post_span": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P],
     "slb_stream_inject": [P, P, P, I, I, P],
     "slb_latent_post": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, P, P, P],
     "slb_head_prompt_attention": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P],
     "slb_latent_attention": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, I, P],
     "slb_latent_gate": [P, P, P, I, I, I, I, P],
-    "slb_moe_route": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, P],
+    "slb_moe_route": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P],
     "slb_moe_experts_tc": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, P, P],
-    "slb_moe_experts": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P],
+    "slb_moe_experts": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, F, I, P],
 }
 
 

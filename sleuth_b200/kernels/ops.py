@@ -18,7 +18,8 @@ import torch
 from . import library
 
 DT = {torch.float32: 0, torch.bfloat16: 1}
-ACTIVATIONS = {"silu": 0, "relu": 1}
+ACTIVATIONS = {"silu": 0, "relu": 1, "clamped_swish": 2}
+ROUTE_SCORINGS = {"softmax_top": 0, "sigmoid": 1}
 
 
 def lib() -> library.KernelLibrary:
@@ -87,13 +88,37 @@ def swiglu(gu: torch.Tensor, act: torch.Tensor, stream=None) -> None:
                stream if stream is not None else current_stream())
 
 
-def gated_act(gu: torch.Tensor, act: torch.Tensor, kind: str = "silu", stream=None) -> None:
-    """act[t, j] = f(gu[t, j]) * gu[t, inter + j] with f = silu or relu."""
+def gated_act(gu: torch.Tensor, act: torch.Tensor, kind: str = "silu", stream=None, limit: float = 0.0,
+              alpha: float = 1.0) -> None:
+    """act[t, j] = f(gu[t, j], gu[t, inter + j]): silu(g) u, relu(g) u, or the clamped swish
+    min(g, limit) sigmoid(alpha min(g, limit)) (clamp(u, -limit, limit) + 1)."""
     _cuda(gu, act)
     T, inter = act.shape
     _need(kind in ACTIVATIONS, f"gated_act: activation {kind!r} is not one of {sorted(ACTIVATIONS)}")
     _need(gu.shape == (T, 2 * inter) and gu.dtype == act.dtype and act.dtype in DT, "gated_act: shapes or dtypes")
-    lib().call("slb_gated_act", _p(gu), _p(act), DT[act.dtype], T, inter, ACTIVATIONS[kind],
+    lib().call("slb_gated_act", _p(gu), _p(act), DT[act.dtype], T, inter, ACTIVATIONS[kind], float(limit), float(alpha),
+               stream if stream is not None else current_stream())
+
+
+def layernorm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, eps: float, rows: torch.Tensor | None = None,
+              stream=None) -> None:
+    """out[r] = (x[row] - mean) / sqrt(var + eps) * w (a gain, no bias); ``out`` may be ``x`` itself."""
+    _cuda(x, w, out, rows)
+    R, d = out.shape
+    _need(x.dtype == torch.float32 and w.dtype == torch.float32 and out.dtype in DT, "layernorm: dtypes")
+    _need(x.shape[1] == d and w.numel() == d, "layernorm: widths disagree")
+    if rows is None:
+        _need(x.shape[0] >= R, "layernorm: fewer input rows than output rows")
+    else:
+        _need(rows.dtype == torch.int32 and rows.numel() >= R, "layernorm: rows must be int32, one per output row")
+    lib().call("slb_layernorm", _p(x), _p(w), _p(out), DT[out.dtype], _p(rows), R, d, float(eps),
+               stream if stream is not None else current_stream())
+
+
+def softcap(v: torch.Tensor, cap: float, stream=None) -> None:
+    """v <- cap * tanh(v / cap) in place; v float32 [rows, cols] with unit column stride."""
+    _need(v.is_cuda and v.dtype == torch.float32 and v.dim() == 2 and v.stride(1) == 1, "softcap: a float32 matrix")
+    lib().call("slb_softcap", _p(v), v.stride(0) if v.shape[0] > 1 else v.shape[1], v.shape[0], v.shape[1], float(cap),
                stream if stream is not None else current_stream())
 
 
@@ -132,17 +157,56 @@ def qkv_post(qkv, bias, q_gain, k_gain, cos, sin, q_out, k_pool, v_pool, tok_seq
                float(eps), DT[qkv.dtype], stream if stream is not None else current_stream())
 
 
+def qkv_post_span(qkv, q_gain, k_gain, cos, sin, q_out, k_pool, v_pool, tok_seq, tok_pos, block_table, heads: int,
+                  kv_heads: int, key_dim: int, value_dim: int, rot_dim: int, neighbours: bool, whole: bool, eps: float,
+                  stream=None) -> None:
+    """What follows separate q, k and v projections whose float32 results lie side by side in ``qkv``
+    [T, heads * key_dim + kv_heads * key_dim + kv_heads * value_dim]: RMS norm of q and k (``whole``: over the whole
+    projection with gains of that length; else per head with gains [key_dim]; no gains: none), rotation of each head's
+    first ``rot_dim`` channels (``neighbours``: pairs (2i, 2i + 1); else (i, i + rot_dim / 2)), q into ``q_out``
+    [T, heads, key_dim], k and v into the token's cache row (pools [pages, kv_heads, 64, key_dim | value_dim])."""
+    _cuda(qkv, q_gain, k_gain, cos, sin, q_out, k_pool, v_pool, tok_seq, tok_pos, block_table)
+    T = q_out.shape[0]
+    _need(qkv.dtype == torch.float32 and qkv.shape == (T, (heads + kv_heads) * key_dim + kv_heads * value_dim),
+          "qkv_post_span: the projections' float32 rows")
+    _need(q_out.shape[1:] == (heads, key_dim) and q_out.dtype in DT, "qkv_post_span: q_out")
+    n_q, n_k = (heads * key_dim, kv_heads * key_dim) if whole else (key_dim, key_dim)
+    for g, n in ((q_gain, n_q), (k_gain, n_k)):
+        _need(g is None or (g.dtype == torch.float32 and g.numel() == n), "qkv_post_span: gains")
+    if rot_dim:
+        _need(cos is not None and cos.dtype == torch.float32 and cos.shape[1] == rot_dim // 2 and sin.shape == cos.shape,
+              "qkv_post_span: rotation tables")
+    stride = 0
+    if k_pool is not None:
+        _need(k_pool.dtype == v_pool.dtype == q_out.dtype and tuple(k_pool.shape[1:]) == (kv_heads, 64, key_dim)
+              and tuple(v_pool.shape[1:]) == (kv_heads, 64, value_dim) and k_pool.shape[0] == v_pool.shape[0],
+              "qkv_post_span: cache pool shape or dtype")
+        _need(block_table.dtype == torch.int32 and block_table.dim() == 2, "qkv_post_span: block table")
+        stride = block_table.shape[1]
+    _need(tok_seq.dtype == torch.int32 and tok_pos.dtype == torch.int32, "qkv_post_span: token tables are int32")
+    lib().call("slb_qkv_post_span", _p(qkv), _p(q_gain), _p(k_gain), _p(cos), _p(sin), _p(q_out), _p(k_pool), _p(v_pool),
+               _p(tok_seq), _p(tok_pos), _p(block_table), stride, T, heads, kv_heads, key_dim, value_dim, rot_dim,
+               1 if neighbours else 0, 1 if whole else 0, float(eps), DT[q_out.dtype],
+               stream if stream is not None else current_stream())
+
+
 def attention(q, k_pool, v_pool, out, tok_seq, tok_pos, block_table, heads: int, kv_heads: int, head_dim: int,
-              window: int, scale: float, stream=None) -> None:
-    _cuda(q, k_pool, v_pool, out, tok_seq, tok_pos, block_table)
+              window: int, scale: float, stream=None, sinks=None, value_dim: int = 0) -> None:
+    """The general attention kernel. ``sinks`` [heads] float32: a learned score per head that joins the softmax
+    denominator (unscaled, once, without a value). ``value_dim``: width of the value rows and of a head's output when it
+    is not ``head_dim``."""
+    _cuda(q, k_pool, v_pool, out, tok_seq, tok_pos, block_table, sinks)
     T = q.shape[0]
-    _need(q.shape == (T, heads, head_dim) and out.shape == (T, heads * head_dim), "attention: shapes disagree")
+    vd = value_dim or head_dim
+    _need(q.shape == (T, heads, head_dim) and out.shape == (T, heads * vd), "attention: shapes disagree")
     _need(q.dtype == out.dtype == k_pool.dtype == v_pool.dtype and q.dtype in DT, "attention: dtypes")
-    _need(tuple(k_pool.shape[1:]) == (kv_heads, 64, head_dim) and k_pool.shape == v_pool.shape, "attention: pool shape")
+    _need(tuple(k_pool.shape[1:]) == (kv_heads, 64, head_dim) and tuple(v_pool.shape[1:]) == (kv_heads, 64, vd)
+          and k_pool.shape[0] == v_pool.shape[0], "attention: pool shape")
     _need(block_table.dtype == torch.int32 and block_table.dim() == 2, "attention: block table")
+    _need(sinks is None or (sinks.dtype == torch.float32 and sinks.numel() == heads), "attention: sinks are float32, one per head")
     lib().call("slb_attention_generic", _p(q), _p(k_pool), _p(v_pool), _p(out), _p(tok_seq), _p(tok_pos),
                _p(block_table), block_table.shape[1], T, heads, kv_heads, head_dim, int(window), float(scale),
-               DT[q.dtype], stream if stream is not None else current_stream())
+               _p(sinks), vd, DT[q.dtype], stream if stream is not None else current_stream())
 
 
 def flash_supported(head_dim: int, dtype: torch.dtype) -> bool:
@@ -790,18 +854,23 @@ MOE_FEW_PAIRS = 64      # up to this many (token, choice) pairs ``moe_experts`` 
 
 
 def moe_route(h, w_router, bias, choice, weight, rank, counts, place, order, top: int, stream=None, logits=None,
-              tiles=None, layout: bool = True) -> None:
-    """Router logits in float32, the ``top`` largest per token, softmax over those; then the (token, choice) pairs are
-    laid out expert by expert: counts [experts], place [T * top] (a pair's row in that order), order [T * top] (the
-    pair at each row). choice, rank int32 [T * top]; weight float32 [T * top]. ``logits``: float32 scratch
-    [T, experts]; with it, steps of many tokens form their logits 32 tokens at a time (the same sums, k ascending).
-    ``layout=False`` leaves counts, place and order unwritten: ``moe_experts`` with ``choice`` does not read them for
-    steps of at most ``MOE_FEW_PAIRS`` pairs."""
+              tiles=None, layout: bool = True, scoring: str = "softmax_top", groups: int = 1, keep: int = 1,
+              scale: float = 1.0) -> None:
+    """Router logits in float32, then the choice. ``scoring="softmax_top"``: the ``top`` largest logits, weights =
+    softmax over those. ``scoring="sigmoid"``: scores = sigmoid(logits); the experts form ``groups`` equal groups of
+    neighbours, a group scores the sum of its two largest scores, only experts of the ``keep`` best groups can be
+    chosen; the ``top`` largest scores, weights = score / (their sum + 1e-20) * ``scale``. Then the (token, choice)
+    pairs are laid out expert by expert: counts [experts], place [T * top] (a pair's row in that order), order
+    [T * top] (the pair at each row). choice, rank int32 [T * top]; weight float32 [T * top]. ``logits``: float32
+    scratch [T, experts]; with it, steps of many tokens form their logits 32 tokens at a time (the same sums, k
+    ascending). ``layout=False`` leaves counts, place and order unwritten: ``moe_experts`` with ``choice`` does not read
+    them for steps of at most ``MOE_FEW_PAIRS`` pairs."""
     _cuda(h, w_router, bias, choice, weight, rank, counts, place, order, logits, tiles)
     T, d = h.shape
     E = w_router.shape[0]
     _need(h.dtype in DT and w_router.dtype == torch.float32 and w_router.shape == (E, d), "moe_route: input or router matrix")
     _need(bias is None or (bias.dtype == torch.float32 and bias.numel() == E), "moe_route: bias")
+    _need(scoring in ROUTE_SCORINGS, f"moe_route: scoring {scoring!r} is not one of {sorted(ROUTE_SCORINGS)}")
     for t in (choice, rank, place, order):
         _need(t.dtype == torch.int32 and t.numel() >= T * top, "moe_route: int32 tables of tokens * top entries")
     _need(weight.dtype == torch.float32 and weight.numel() >= T * top and counts.dtype == torch.int32 and counts.numel() >= E,
@@ -809,11 +878,12 @@ def moe_route(h, w_router, bias, choice, weight, rank, counts, place, order, top
     _need(logits is None or (logits.dtype == torch.float32 and logits.numel() >= T * E), "moe_route: scratch for the logits")
     _need(tiles is None or (tiles.dtype == torch.int32 and tiles.numel() >= moe_tile_words(T, top, E)), "moe_route: row-tile table")
     lib().call("slb_moe_route", _p(h), _p(w_router), _p(bias), _p(choice), _p(weight), _p(rank), _p(counts), _p(place),
-               _p(order), _p(logits), _p(tiles), 1 if layout else 0, T, d, E, int(top), DT[h.dtype], stream if stream is not None else current_stream())
+               _p(order), _p(logits), _p(tiles), 1 if layout else 0, T, d, E, int(top), ROUTE_SCORINGS[scoring], int(groups),
+               int(keep), float(scale), DT[h.dtype], stream if stream is not None else current_stream())
 
 
 def moe_experts(h, w_gate_up, w_down, counts, order, weight, act, y, x, top: int, activation: str = "silu",
-                stream=None, choice=None, place=None) -> None:
+                stream=None, choice=None, place=None, limit: float = 0.0, alpha: float = 1.0) -> None:
     """x[t] += sum over the token's choices of weight * down_e(f(gate_e h) * (up_e h)). w_gate_up [experts, 2 * ff, d]
     (gate rows, then up rows), w_down [experts, d, ff]; act [T * top, ff] and y [T * top, d] float32 are scratch.
     With ``choice`` and ``place`` (from ``moe_route``) a step of few pairs runs a warp per output instead of tiles."""
@@ -829,7 +899,7 @@ def moe_experts(h, w_gate_up, w_down, counts, order, weight, act, y, x, top: int
     _need(x.shape == (T, d) and x.dtype == torch.float32, "moe_experts: the stream")
     _need(activation in ACTIVATIONS, f"moe_experts: activation {activation!r}")
     lib().call("slb_moe_experts", _p(h), _p(w_gate_up), _p(w_down), _p(counts), _p(order), _p(choice), _p(place), _p(weight), _p(act), _p(y),
-               _p(x), T, d, ff, E, int(top), ACTIVATIONS[activation], DT[h.dtype],
+               _p(x), T, d, ff, E, int(top), ACTIVATIONS[activation], float(limit), float(alpha), DT[h.dtype],
                stream if stream is not None else current_stream())
 
 

@@ -9,6 +9,12 @@ head mapping :197-199, window mask :160-169, output projection without bias :155
 
 With ``reads_shared_kv`` the part has no k/v projections and reads the cache entry another layer
 application wrote.
+
+Options that another design may set (``AttentionSpec``): values of another width than the keys (``value_dim``), one
+RMSNorm over the whole q projection and one over the whole k projection instead of one per head
+(``qk_norm_span="projection"``), rotation of neighbouring channels (the position's ``pairing``), and a learned sink per
+head in the softmax denominator (``sinks``). Any of the first three sends a step through the *wide* form: the stacked
+projection with a float32 result, ``qkv_post_span`` (norms, rotation, cache write) and the attention kernel.
 """
 
 from __future__ import annotations
@@ -46,30 +52,43 @@ class GQAAttention(Part):
             raise ValueError(f"heads ({spec.heads}) must be a multiple of kv_heads ({spec.kv_heads})")
         if spec.head_dim % 2 or spec.head_dim > 256:
             raise ValueError(f"head_dim {spec.head_dim} is not supported: it must be even and at most 256")
+        if spec.qk_norm_span not in ("head", "projection"):
+            raise ValueError(f"qk_norm_span {spec.qk_norm_span!r} is not 'head' or 'projection'")
         self.spec = spec
         self.ctx = ctx
         self.position = build_position(spec.position, ctx)
         self.scale = spec.scale or 1.0 / math.sqrt(spec.head_dim)
         self.qkv = self.o = None
-        self.bias = self.q_gain = self.k_gain = None
+        self.bias = self.q_gain = self.k_gain = self.sinks = None
+        self.value_dim = spec.value_dim or spec.head_dim
+        if self.value_dim > 256:
+            raise ValueError(f"value_dim {self.value_dim} is not supported: at most 256")
+        self.whole_norm = spec.qk_norm and spec.qk_norm_span == "projection"
+        # the wide form: what the per-head kernels (equal widths, per-head norms, halves turned together) do not take
+        self.wide = (self.value_dim != spec.head_dim or self.whole_norm or getattr(self.position, "neighbours", False))
+        if self.wide and (spec.qkv_bias or spec.reads_shared_kv):
+            raise ValueError("attention: biases and a borrowed cache entry are not built for values of another width, "
+                             "whole-projection norms or neighbour pairing")
 
     # ---- weights ----
     def declare(self):
         s = self.spec
         d = {"q_proj.weight": ParamDecl((s.heads * s.head_dim, s.hidden)),
-             "o_proj.weight": ParamDecl((s.hidden, s.heads * s.head_dim))}
+             "o_proj.weight": ParamDecl((s.hidden, s.heads * self.value_dim))}
         if not s.reads_shared_kv:
             d["k_proj.weight"] = ParamDecl((s.kv_heads * s.head_dim, s.hidden))
-            d["v_proj.weight"] = ParamDecl((s.kv_heads * s.head_dim, s.hidden))
+            d["v_proj.weight"] = ParamDecl((s.kv_heads * self.value_dim, s.hidden))
         if s.qkv_bias:
             d["q_proj.bias"] = ParamDecl((s.heads * s.head_dim,), "vector")
             if not s.reads_shared_kv:
                 d["k_proj.bias"] = ParamDecl((s.kv_heads * s.head_dim,), "vector")
                 d["v_proj.bias"] = ParamDecl((s.kv_heads * s.head_dim,), "vector")
         if s.qk_norm:
-            d["q_norm.weight"] = ParamDecl((s.head_dim,), "vector", init="gain")
+            d["q_norm.weight"] = ParamDecl(((s.heads if self.whole_norm else 1) * s.head_dim,), "vector", init="gain")
             if not s.reads_shared_kv:
-                d["k_norm.weight"] = ParamDecl((s.head_dim,), "vector", init="gain")
+                d["k_norm.weight"] = ParamDecl(((s.kv_heads if self.whole_norm else 1) * s.head_dim,), "vector", init="gain")
+        if s.sinks:
+            d["sinks"] = ParamDecl((s.heads,), "vector")
         return d
 
     def bind(self, t):
@@ -82,19 +101,21 @@ class GQAAttention(Part):
         if s.qk_norm:
             self.q_gain = t["q_norm.weight"]
             self.k_gain = t["q_norm.weight"] if s.reads_shared_kv else t["k_norm.weight"]
+        if s.sinks:
+            self.sinks = t["sinks"].to(torch.float32).contiguous()
 
     def cache_request(self):
         s = self.spec
-        return KVRequest(s.kv_heads, s.head_dim, s.window)
+        return KVRequest(s.kv_heads, s.head_dim, s.window, 0 if self.value_dim == s.head_dim else self.value_dim)
 
     # ---- one step ----
     def _attend(self, q, y, b, view, table, ws):
         """Attention of the step's (post-processed) queries over the cache into ``y``; the kernel by dtype and step shape."""
         s = self.spec
-        flash = ops.flash_supported(s.head_dim, self.ctx.dtype)
+        flash = ops.flash_supported(s.head_dim, self.ctx.dtype) and self.value_dim == s.head_dim and self.sinks is None
         if not flash:
             ops.attention(q, view.k_pool, view.v_pool, y, b.tok_seq, b.tok_pos, table, s.heads, s.kv_heads,
-                          s.head_dim, view.window, self.scale, b.stream)
+                          s.head_dim, view.window, self.scale, b.stream, sinks=self.sinks, value_dim=self.value_dim)
         elif b.max_count == 1:
             splits = ops.decode_splits(b.n, s.kv_heads, s.heads // s.kv_heads, table.shape[1])
             floats = ops.decode_scratch_floats(b.n, s.heads, s.head_dim, splits)
@@ -114,7 +135,7 @@ class GQAAttention(Part):
     def fused_decode(self):
         s = self.spec
         rot = self.position.rot_dim
-        if (self.ctx.dtype != torch.bfloat16 or self.qkv is None or s.reads_shared_kv or s.head_dim not in (64, 128)
+        if (self.wide or self.sinks is not None or self.ctx.dtype != torch.bfloat16 or self.qkv is None or s.reads_shared_kv or s.head_dim not in (64, 128)
                 or rot not in (0, s.head_dim) or s.heads // s.kv_heads > 8 or s.hidden % 128
                 or (s.qk_norm and (self.q_gain is None or self.k_gain is None))):
             return None
@@ -134,7 +155,11 @@ class GQAAttention(Part):
         tables = self.position.tables()
         cos, sin = tables if tables is not None else (None, None)
         rot = self.position.rot_dim
-        flash = ops.flash_supported(s.head_dim, self.ctx.dtype)
+        if self.wide:
+            self._forward_wide(h, x, b, view, table, cos, sin, rot, ws)
+            ws.release(mark)
+            return
+        flash = ops.flash_supported(s.head_dim, self.ctx.dtype) and self.sinks is None
         fused_post = (flash and rot in (0, s.head_dim) and b.max_count > 1 and (writes or s.reads_shared_kv)
                       and use_tc(T, self.qkv.out_features, self.qkv.in_features))
         if fused_post:
@@ -177,6 +202,23 @@ class GQAAttention(Part):
         self._attend(q, y, b, view, table, ws)
         self.o.forward(y, into=x, ws=ws, stream=b.stream)
         ws.release(mark)
+
+
+    def _forward_wide(self, h, x, b, view, table, cos, sin, rot, ws):
+        """The wide form: the stacked projection's float32 rows, then norms, rotation and the cache write in one kernel
+        on those rows (one rounding, at the store), then attention over the cache and the output projection."""
+        s = self.spec
+        T = h.shape[0]
+        qkv = self.qkv.forward(h, ws=ws, stream=b.stream, out_dtype=torch.float32)
+        q = ws.take((T, s.heads, s.head_dim), self.ctx.dtype)
+        writes = view.writes
+        ops.qkv_post_span(qkv, self.q_gain, self.k_gain, cos if rot else None, sin if rot else None, q,
+                          view.k_pool if writes else None, view.v_pool if writes else None, b.tok_seq, b.tok_pos, table,
+                          s.heads, s.kv_heads, s.head_dim, self.value_dim, rot, self.position.neighbours, self.whole_norm,
+                          s.qk_norm_eps, b.stream)
+        y = ws.take((T, s.heads * self.value_dim), self.ctx.dtype)
+        self._attend(q, y, b, view, table, ws)
+        self.o.forward(y, into=x, ws=ws, stream=b.stream, next_read=getattr(b, "next_read", None))
 
 
 register_mixer("gqa_attention", GQAAttention)

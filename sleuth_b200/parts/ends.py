@@ -11,27 +11,37 @@ from .spec import EmbeddingSpec, HeadSpec
 
 
 class TokenEmbedding(Part):
-    """x[t] = table[ids[t]] * scale into the float32 stream (sleuth/forge/model/transformer.py:345-348)."""
+    """x[t] = table[ids[t]] * scale into the float32 stream (sleuth/forge/model/transformer.py:345-348); with
+    ``spec.norm`` the rows are then normalised in place, in float32."""
 
     def __init__(self, spec: EmbeddingSpec, ctx: BuildContext):
         self.spec, self.ctx = spec, ctx
         self.table = None
+        self.norm = build_norm(spec.norm, ctx) if spec.norm is not None else None
 
     def declare(self):
-        return {"weight": ParamDecl((self.spec.vocab, self.spec.dim))}
+        d = {"weight": ParamDecl((self.spec.vocab, self.spec.dim))}
+        if self.norm is not None:
+            d["norm.weight"] = ParamDecl((self.spec.dim,), "vector", init="gain")
+        return d
 
     def bind(self, t):
         self.table = t["weight"]
+        if self.norm is not None:
+            self.norm.bind({"weight": t["norm.weight"]})
 
     def forward(self, b, x):
         """``b``: the step's batch; its token ids sit in ``b.token_ids`` (read through ``b.ids_map`` in a step that
         takes its tokens from the device-side feed)."""
         ops.embed(b.token_ids, self.table, x, self.spec.scale, b.stream, b.ids_map)
+        if self.norm is not None:
+            self.norm.forward(x, x, stream=b.stream)
 
 
 class LMHead(Part):
     """Final norm on the chosen rows, then logits = h @ W^T in float32
-    (sleuth/forge/model/transformer.py:301-302). A tied head uses the embedding table (:129-130)."""
+    (sleuth/forge/model/transformer.py:301-302). A tied head uses the embedding table (:129-130). With
+    ``spec.softcap`` = c the logits become c * tanh(logits / c)."""
 
     def __init__(self, spec: HeadSpec, ctx: BuildContext):
         self.spec, self.ctx = spec, ctx
@@ -55,6 +65,8 @@ class LMHead(Part):
         h = ws.take((logits.shape[0], self.spec.dim), self.ctx.dtype)
         self.norm.forward(x, h, b.rows, b.stream)
         self.proj.forward(h, out=logits, stream=b.stream)
+        if self.spec.softcap > 0:
+            ops.softcap(logits, self.spec.softcap, b.stream)
         ws.release(mark)
 
 

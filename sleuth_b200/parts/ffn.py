@@ -1,5 +1,5 @@
-"""Feed-forward parts. ``gated_mlp``: down(act(gate(h)) * up(h)) without biases, act = silu
-(sleuth/forge/model/mlp.py:25-41) or relu (product, then the gated-activation kernel). Gate and up matrices are stacked at load time into one
+"""Feed-forward parts. ``gated_mlp``: down(f(gate(h), up(h))) without biases, f = silu(g) u
+(sleuth/forge/model/mlp.py:25-41), relu(g) u or the clamped swish (product, then the gated-activation kernel). Gate and up matrices are stacked at load time into one
 ``[2 * intermediate, hidden]`` matrix, so one product feeds the activation kernel."""
 
 from __future__ import annotations
@@ -26,6 +26,8 @@ class GatedMLP(Part):
     def __init__(self, spec: GatedMLPSpec, ctx: BuildContext):
         if spec.activation not in ops.ACTIVATIONS:
             raise ValueError(f"gated_mlp: activation {spec.activation!r} is not supported ({sorted(ops.ACTIVATIONS)})")
+        if spec.activation == "clamped_swish" and not spec.limit > 0:
+            raise ValueError(f"gated_mlp: the clamped swish needs a positive limit, got {spec.limit}")
         self.silu = spec.activation == "silu"     # the products' fused epilogues know this gate only
         self.spec, self.ctx = spec, ctx
         self.gate_up = self.down = None
@@ -54,7 +56,7 @@ class GatedMLP(Part):
         act = ws.take((T, self.spec.intermediate), self.ctx.dtype)
         if not self.silu:
             gu = self.gate_up.forward(h, ws=ws, stream=b.stream)
-            ops.gated_act(gu, act, self.spec.activation, b.stream)
+            ops.gated_act(gu, act, self.spec.activation, b.stream, self.spec.limit, self.spec.alpha)
         elif self.ctx.dtype == torch.bfloat16 and linear.use_skinny(T, self.spec.intermediate, self.spec.hidden):
             # norm in the product's prologue (when handed the stream), activation in its epilogue
             if (isinstance(h, Normed) and h.gain is not None and FUSE_NORM

@@ -1,6 +1,7 @@
 """Arrangements of a mixer, a feed-forward and their norms in one layer.
 
-``parallel``: h = norm1(x); x += mixer(h) + ffn(h) (one norm; the feed-forward may be absent).
+``parallel``: x += mixer(norm1(x)) + ffn(norm2(x)), both sublayers reading the same x; with one norm
+(``norm2`` absent) the feed-forward reads norm1's output too; the feed-forward may be absent.
 
 ``prenorm``: x += mixer(norm1(x)); x += ffn(norm2(x)) (sleuth/forge/model/transformer.py:78,87-88,96,99).
 The layer owns the residual arrangement only; the parts it is given decide everything else. The sum
@@ -68,15 +69,19 @@ class PreNormLayer(Part):
 
 
 class ParallelLayer(Part):
-    """h = norm1(x); x += mixer(h) + ffn(h): one norm, both sublayers read its output, and each adds its result into
-    the float32 stream. The feed-forward may be absent."""
+    """x += mixer(norm1(x)) + ffn(norm2(x)): both sublayers read the same x and each adds its result into the float32
+    stream, so both norms run before either sublayer does. With one norm (no ``norm2``) the feed-forward reads norm1's
+    output. The feed-forward may be absent."""
 
     def __init__(self, spec: LayerSpec, ctx: BuildContext):
         self.ctx = ctx
         self.norm1 = build_norm(spec.norm1, ctx)
         self.mixer = build_mixer(spec.mixer, ctx)
         self.ffn = build_ffn(spec.ffn, ctx) if spec.ffn is not None else None
+        self.norm2 = build_norm(spec.norm2, ctx) if (spec.norm2 is not None and self.ffn is not None) else None
         self.children = {"norm1": self.norm1, "mixer": self.mixer}
+        if self.norm2 is not None:
+            self.children["norm2"] = self.norm2
         if self.ffn is not None:
             self.children["ffn"] = self.ffn
         self.capturable = all(getattr(p, "capturable", True) for p in self.children.values())
@@ -90,11 +95,13 @@ class ParallelLayer(Part):
         mark = ws.mark()
         after = getattr(b, "next_read", None)
         h = Normed(self.norm1, x, ws, b.stream, self.ctx.dtype).tensor()
+        # the feed-forward's input is formed before the mixer adds into the stream
+        h2 = Normed(self.norm2, x, ws, b.stream, self.ctx.dtype).tensor() if self.norm2 is not None else h
         b.next_read = lead_weight_of(self.ffn) if self.ffn is not None else after
         self.mixer.forward(h, x, b, view, ws)
         b.next_read = after
         if self.ffn is not None:
-            self.ffn.forward(h, x, b, ws)
+            self.ffn.forward(h2, x, b, ws)
         ws.release(mark)
 
 

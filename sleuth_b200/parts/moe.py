@@ -1,8 +1,11 @@
 """Routed experts as a feed-forward part.
 
 Router logits z = W_r h + b in float32 (W_r and b are kept in float32; h is the layer's normed input in the run
-dtype). A token uses the ``top`` experts with the largest logits, weighted by the softmax over those logits alone,
-and an expert is down(act(gate h) * (up h)). The part's output, the weighted sum, is added into the stream.
+dtype). A token uses the ``top`` experts with the largest logits, weighted by the softmax over those logits alone, or
+(``scoring="sigmoid"``) those with the largest sigmoid scores among the best groups of neighbouring experts, weighted
+by score / sum of the chosen scores, scaled; an expert is down(f(gate h, up h)) with one of the gated activations. The
+part's output, the weighted sum (plus a shared expert that every token runs, when the spec names one), is added into
+the stream.
 
 The experts' matrices are stacked at load time ([experts, 2 * ff, hidden] for gate and up, [experts, hidden, ff]
 for down). A step runs five kernels (``csrc/moe.cu``): router, the counts and the expert-ordered list of (token,
@@ -17,7 +20,7 @@ from __future__ import annotations
 import torch
 
 from ..kernels import ops
-from .base import BuildContext, Normed, ParamDecl, Part, register_ffn
+from .base import BuildContext, Normed, ParamDecl, Part, build_ffn, register_ffn
 from .spec import RoutedExpertsSpec
 
 
@@ -32,8 +35,22 @@ class RoutedExperts(Part):
             raise ValueError(f"routed_experts: activation {spec.activation!r} is not supported ({sorted(ops.ACTIVATIONS)})")
         if not 0 < spec.top <= spec.experts:
             raise ValueError(f"routed_experts: top {spec.top} of {spec.experts} experts")
+        if spec.scoring not in ops.ROUTE_SCORINGS:
+            raise ValueError(f"routed_experts: scoring {spec.scoring!r} is not one of {sorted(ops.ROUTE_SCORINGS)}")
+        if spec.groups < 1 or spec.experts % spec.groups or not 1 <= spec.keep_groups <= spec.groups:
+            raise ValueError(f"routed_experts: {spec.experts} experts in {spec.groups} groups of which {spec.keep_groups} are kept")
+        if spec.groups > 1 and spec.scoring != "sigmoid":
+            raise ValueError("routed_experts: groups of experts go with the sigmoid scoring")
+        if spec.keep_groups * (spec.experts // spec.groups) < spec.top:
+            raise ValueError(f"routed_experts: {spec.keep_groups} groups of {spec.experts // spec.groups} experts cannot give {spec.top} choices")
+        if spec.activation == "clamped_swish" and not spec.limit > 0:
+            raise ValueError(f"routed_experts: the clamped swish needs a positive limit, got {spec.limit}")
         self.spec, self.ctx = spec, ctx
         self.w_router = self.bias = self.w_gate_up = self.w_down = None
+        self.shared = build_ffn(spec.shared, ctx) if spec.shared is not None else None
+
+    def lead_weight(self):
+        return self.shared.lead_weight() if self.shared is not None else None
 
     def declare(self):
         s = self.spec
@@ -44,6 +61,9 @@ class RoutedExperts(Part):
             d[f"e{e}.gate.weight"] = ParamDecl((s.intermediate, s.hidden))
             d[f"e{e}.up.weight"] = ParamDecl((s.intermediate, s.hidden))
             d[f"e{e}.down.weight"] = ParamDecl((s.hidden, s.intermediate))
+        if self.shared is not None:
+            for name, decl in self.shared.declare().items():
+                d["shared." + name] = decl
         return d
 
     def bind(self, t):
@@ -53,11 +73,18 @@ class RoutedExperts(Part):
         self.w_gate_up = torch.stack([torch.cat([t[f"e{e}.gate.weight"], t[f"e{e}.up.weight"]], dim=0)
                                       for e in range(s.experts)]).to(dt).contiguous()
         self.w_down = torch.stack([t[f"e{e}.down.weight"] for e in range(s.experts)]).to(dt).contiguous()
+        if self.shared is not None:
+            self.shared.bind({k[len("shared."):]: v for k, v in t.items() if k.startswith("shared.")})
 
     def forward(self, h, x, b, ws):
         s, dt = self.spec, self.ctx.dtype
         if isinstance(h, Normed):
             h = h.tensor()
+        if self.shared is not None:       # the shared expert first: its weights are what the layer in front asked L2 for
+            after = getattr(b, "next_read", None)
+            b.next_read = None
+            self.shared.forward(h, x, b, ws)
+            b.next_read = after
         T = h.shape[0]
         pairs = T * s.top
         mark = ws.mark()
@@ -72,13 +99,14 @@ class RoutedExperts(Part):
                    and s.intermediate % 8 == 0)
         tiles = ws.take((ops.moe_tile_words(T, s.top, s.experts),), torch.int32) if grouped else None
         ops.moe_route(h, self.w_router, self.bias, choice, weight, rank, counts, place, order, s.top, b.stream, logits, tiles,
-                      layout=pairs > ops.MOE_FEW_PAIRS)
+                      layout=pairs > ops.MOE_FEW_PAIRS, scoring=s.scoring, groups=s.groups, keep=s.keep_groups,
+                      scale=s.route_scale)
         if grouped:
             xs = ws.take((pairs, s.hidden), dt)
             ops.moe_experts_tc(h, self.w_gate_up, self.w_down, order, place, weight, tiles, xs, act, y, x, s.top, b.stream)
         else:
             ops.moe_experts(h, self.w_gate_up, self.w_down, counts, order, weight, act, y, x, s.top, s.activation, b.stream,
-                            choice, place)
+                            choice, place, limit=s.limit, alpha=s.alpha)
         ws.release(mark)
 
 

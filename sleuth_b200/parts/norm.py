@@ -1,5 +1,6 @@
 """Normalisation parts. ``rmsnorm``: y = x * rsqrt(mean(x^2) + eps) * gain, float32 arithmetic on the
-float32 stream, output in the run dtype (sleuth/forge/model/norm.py:34-50)."""
+float32 stream, output in the run dtype (sleuth/forge/model/norm.py:34-50). ``layernorm``: y = (x - mean) /
+sqrt(var + eps) * gain with var the mean of the squared deviations and no bias, the same way."""
 
 from __future__ import annotations
 
@@ -32,4 +33,25 @@ class RMSNorm(Part):
         return out
 
 
+class LayerNorm(Part):
+    """Layer norm with a gain and no bias. ``out`` may be float32 (and the stream itself: a row is read whole before it
+    is written)."""
+    fusable = False
+
+    def __init__(self, spec: NormSpec, ctx: BuildContext):
+        self.dim, self.eps, self.dtype = spec.dim, spec.eps, ctx.dtype
+        self.weight = None
+
+    def declare(self):
+        return {"weight": ParamDecl((self.dim,), "vector", init="gain")}
+
+    def bind(self, tensors):
+        self.weight = tensors["weight"]
+
+    def forward(self, x: torch.Tensor, out: torch.Tensor, rows: torch.Tensor | None = None, stream=None):
+        ops.layernorm(x, self.weight, out, self.eps, rows, stream)
+        return out
+
+
 register_norm("rmsnorm", RMSNorm)
+register_norm("layernorm", LayerNorm)

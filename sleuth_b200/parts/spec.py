@@ -20,6 +20,8 @@ from typing import Mapping
 
 @dataclass(frozen=True)
 class NormSpec:
+    """``kind="rmsnorm"``: x / sqrt(mean(x^2) + eps) * gain. ``kind="layernorm"``: (x - mean) / sqrt(var + eps) * gain,
+    var the mean of the squared deviations, no bias."""
     dim: int
     eps: float
     kind: str = "rmsnorm"
@@ -27,12 +29,16 @@ class NormSpec:
 
 @dataclass(frozen=True)
 class PositionSpec:
-    """Position encoding applied to queries and keys. ``kind="rotary"``: rotate-half pairs (i, i+rot/2)
-    over the first ``rotary_dim`` channels of each head; ``kind="none"``: nothing."""
+    """Position encoding applied to queries and keys. ``kind="rotary"``: the first ``rotary_dim`` channels of each
+    head turn in pairs by the angle position * theta^(-2i/rotary_dim) of pair i; ``pairing="halves"`` pairs channel i
+    with i + rotary_dim/2, ``pairing="neighbours"`` channel 2i with 2i + 1. ``kind="none"``: nothing.
+    ``precise``: the tables are worked out in 64-bit and rounded once (otherwise in float32, operation by operation)."""
     head_dim: int
     theta: float = 10000.0
     rotary_dim: int = 0          # 0 = all of head_dim
     kind: str = "rotary"
+    pairing: str = "halves"
+    precise: bool = False
 
 
 @dataclass(frozen=True)
@@ -50,6 +56,10 @@ class AttentionSpec:
     scale: float = 0.0           # 0 = 1/sqrt(head_dim)
     reads_shared_kv: bool = False  # no k/v projections: reads the cache another layer application wrote
     kind: str = "gqa_attention"
+    value_dim: int = 0           # width of a head's values and output; 0 = head_dim
+    qk_norm_span: str = "head"   # "head": one RMSNorm per head, gains [head_dim]; "projection": one over all heads of q
+                                 # (and one over all heads of k) before they are split, gains of the projection's length
+    sinks: bool = False          # a learned score per head joins the softmax denominator (no key, no value, unscaled)
 
 
 @dataclass(frozen=True)
@@ -77,17 +87,25 @@ class LatentAttentionSpec:
 
 @dataclass(frozen=True)
 class GatedMLPSpec:
-    """down(act(gate(x)) * up(x)), no biases; ``activation``: "silu" or "relu"."""
+    """down(f(gate(x), up(x))), no biases; ``activation``: "silu" (silu(g) u), "relu" (relu(g) u) or "clamped_swish"
+    (g' = min(g, limit), u' = clamp(u, -limit, limit): g' sigmoid(alpha g') (u' + 1))."""
     hidden: int
     intermediate: int
     activation: str = "silu"
     kind: str = "gated_mlp"
+    limit: float = 0.0
+    alpha: float = 1.0
 
 
 @dataclass(frozen=True)
 class RoutedExpertsSpec:
-    """``experts`` gated feed-forwards of ``intermediate`` channels, of which a token uses the ``top`` with the
-    largest router logits (W_r h + b, float32), weighted by the softmax over those logits alone."""
+    """``experts`` gated feed-forwards of ``intermediate`` channels, of which a token uses ``top``.
+    ``scoring="softmax_top"``: those with the largest router logits (W_r h + b, float32), weighted by the softmax over
+    those logits alone. ``scoring="sigmoid"``: scores = sigmoid(logits); the experts form ``groups`` equal groups of
+    neighbours, a group scores the sum of its two largest scores, and only experts of the ``keep_groups`` best groups
+    can be chosen; the ``top`` largest scores, weights = score / (their sum + 1e-20) * ``route_scale``.
+    ``activation``, ``limit``, ``alpha``: as for ``GatedMLPSpec``. ``shared``: a gated feed-forward (a ``GatedMLPSpec``)
+    that every token runs and whose output is added, or None."""
     hidden: int
     intermediate: int
     experts: int
@@ -95,12 +113,20 @@ class RoutedExpertsSpec:
     activation: str = "silu"
     router_bias: bool = True
     kind: str = "routed_experts"
+    limit: float = 0.0
+    alpha: float = 1.0
+    scoring: str = "softmax_top"
+    groups: int = 1
+    keep_groups: int = 1
+    route_scale: float = 1.0
+    shared: object = None
 
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One layer: an arrangement (``kind``) of a mixer, a feed-forward and their norms. ``kind="parallel"`` has one
-    norm (``norm2`` is None) and may have no feed-forward (``ffn`` is None).
+    """One layer: an arrangement (``kind``) of a mixer, a feed-forward and their norms. ``kind="parallel"``:
+    x += mixer(norm1 x) + ffn(norm2 x), both of the same x; without ``norm2`` (None) the feed-forward reads norm1's
+    output too; it may have no feed-forward (``ffn`` is None).
 
     ``names`` maps each part-local tensor name ("norm1.weight", "mixer.q_proj.weight",
     "ffn.down.weight", ...) to its name in the weight files."""
@@ -135,6 +161,8 @@ class EmbeddingSpec:
     scale: float = 1.0
     name: str = "model.embed_tokens.weight"
     kind: str = "token_embedding"
+    norm: NormSpec | None = None          # a norm applied to the looked-up rows (its gain is the tensor ``norm.weight``)
+    norm_name: str = "model.embed_norm.weight"
 
 
 @dataclass(frozen=True)
@@ -149,6 +177,7 @@ class HeadSpec:
     norm_name: str = "model.norm.weight"
     name: str = "lm_head.weight"
     kind: str = "lm_head"
+    softcap: float = 0.0         # c > 0: logits <- c * tanh(logits / c)
 
 
 @dataclass(frozen=True)
@@ -193,6 +222,12 @@ def looped_schedule(n_layers: int, start: int, stop: int, times: int) -> tuple:
         out.append(ScheduleEntry(i, cache))
         cache += 1
     return tuple(out)
+
+
+def shared_weight_schedule(owners) -> tuple:
+    """``owners[i]``: index (among the model's layers, which hold weights) of the layer whose weights application i uses.
+    Every application has a cache entry of its own."""
+    return tuple(ScheduleEntry(int(o), i) for i, o in enumerate(owners))
 
 
 def straight_schedule(n_layers: int) -> tuple:
