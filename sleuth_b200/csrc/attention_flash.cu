@@ -55,7 +55,11 @@ struct FlashArgs {
   float eps;
   int qkv_kv_heads;             // key/value heads present in qkv (0: this layer reads another layer's cache)
   int pages_after_wait;         // 1: no cache page is asked for before the kernel in front has completed (see the kernel)
+  const float* sinks;           // [H] or null: a learned score per head that joins the softmax denominator once,
+                                // unscaled, without a key or a value
 };
+
+constexpr float kLog2e = 1.4426950408889634f;
 
 // byte offset of element (row, col) in a swizzled [rows][HD] bf16 tile; col is a multiple of 8
 template <int HD> __device__ __forceinline__ uint32_t swz(int row, int col) {
@@ -256,6 +260,7 @@ __global__ void __launch_bounds__(kFlashThreads) attn_prefill_kernel(FlashArgs a
   for (int h = 0; h < 2; ++h) {
     const int R = r0 + warp * 16 + g + 8 * h;
     if (R >= rows_total) continue;
+    if (a.sinks) l_r[h] += exp2f(a.sinks[kh * G + R % G] * kLog2e - m_r[h]);
     const float inv = 1.0f / l_r[h];
     __nv_bfloat16* dst = a.out + ((size_t)(tok0 + R / G) * a.heads + kh * G + R % G) * HD;
 #pragma unroll
@@ -572,6 +577,7 @@ __global__ void __launch_bounds__(kFlashThreads) attn_decode_kernel(FlashArgs a)
     }
     const int head = head0 + row;
     if (a.splits == 1) {
+      if (a.sinks) l += exp2f(a.sinks[head] * kLog2e - m_use);
       a.out[((size_t)tok * a.heads + head) * HD + d] = __float2bfloat16_rn(acc / l);
     } else {
       const size_t pi = ((size_t)seq * a.heads + head) * a.splits + split;
@@ -628,6 +634,7 @@ __global__ void __launch_bounds__(kFlashThreads) attn_decode_kernel(FlashArgs a)
       }
       m = m_new;
     }
+    if (a.sinks) l += exp2f(a.sinks[head] * kLog2e - m);
     a.out[((size_t)tok * a.heads + head) * HD + d] = __float2bfloat16_rn(acc / l);
   }
   if (tid == 0) *counter = 0;
@@ -702,7 +709,7 @@ extern "C" long long slb_attention_decode_scratch_floats(int n_seqs, int heads, 
 extern "C" int slb_attention_prefill(const void* q, const void* k_pool, const void* v_pool, void* out,
                                      const int* seq_start, const int* past, const int* counts, const int* block_table,
                                      int table_stride, int n_seqs, int max_count, int heads, int kv_heads, int head_dim,
-                                     int window, float scale, void* stream) {
+                                     int window, float scale, const float* sinks, void* stream) {
   SLB_REQUIRE(n_seqs >= 0 && max_count >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0,
               "attention (prefill): seqs=%d max_count=%d heads=%d kv_heads=%d", n_seqs, max_count, heads, kv_heads);
   SLB_REQUIRE(head_dim == 64 || head_dim == 128, "attention (prefill): the tensor-core kernel takes head_dim 64 or 128, got %d", head_dim);
@@ -712,7 +719,7 @@ extern "C" int slb_attention_prefill(const void* q, const void* k_pool, const vo
   a.q = (const __nv_bfloat16*)q; a.k_pool = (const __nv_bfloat16*)k_pool; a.v_pool = (const __nv_bfloat16*)v_pool;
   a.out = (__nv_bfloat16*)out; a.seq_start = seq_start; a.past = past; a.counts = counts;
   a.block_table = block_table; a.table_stride = table_stride; a.heads = heads; a.kv_heads = kv_heads;
-  a.window = window; a.scale_log2 = scale * 1.4426950408889634f; a.splits = 1;
+  a.window = window; a.scale_log2 = scale * 1.4426950408889634f; a.splits = 1; a.sinks = sinks;
   return head_dim == 64 ? launch_prefill<64>(a, n_seqs, max_count, (cudaStream_t)stream)
                         : launch_prefill<128>(a, n_seqs, max_count, (cudaStream_t)stream);
 }
@@ -724,7 +731,7 @@ extern "C" int slb_attention_decode(const void* q, const void* k_pool, const voi
                                     long long n_counters, const void* qkv, int qkv_kv_heads, const float* bias,
                                     const float* q_gain, const float* k_gain, const float* cos_table,
                                     const float* sin_table, float eps, const void* next, long long next_bytes,
-                                    void* stream) {
+                                    const float* sinks, void* stream) {
   // qkv != null: `q` is ignored; the kernel takes the new token's raw projection rows [n, (H + 2 * qkv_kv_heads) * hd],
   // applies bias, QK-norm and the rotation itself, and (qkv_kv_heads == kv_heads) writes the token's key and value
   // into the cache. cos/sin tables, if given, are [positions, hd / 2]: the whole head rotates.
@@ -754,7 +761,7 @@ extern "C" int slb_attention_decode(const void* q, const void* k_pool, const voi
   a.part_o = scratch;
   a.part_ml = scratch ? scratch + (size_t)n_seqs * heads * splits * head_dim : nullptr;
   a.qkv = (const __nv_bfloat16*)qkv; a.qkv_kv_heads = qkv_kv_heads; a.bias = bias; a.q_gain = q_gain; a.k_gain = k_gain;
-  a.cos_table = cos_table; a.sin_table = sin_table; a.eps = eps;
+  a.cos_table = cos_table; a.sin_table = sin_table; a.eps = eps; a.sinks = sinks;
   a.pages_after_wait = (qkv == nullptr || qkv_kv_heads == 0 || pdl_mode() == 1) ? 1 : 0;
   SLB_REQUIRE(next_bytes >= 0 && (uintptr_t)next % 16 == 0, "attention (decode): the range to prefetch must be 16-byte aligned");
   a.next.ptr = (const char*)next; a.next.bytes = next ? next_bytes : 0;

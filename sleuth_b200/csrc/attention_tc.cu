@@ -52,6 +52,7 @@ struct AttnTcArgs {
   int heads, kv_heads, window;
   float scale_log2;
   int* status;
+  const float* sinks;           // [H] or null: a learned score per head that joins the softmax denominator once, unscaled
 };
 
 __device__ __forceinline__ float ex2(float x) {
@@ -380,6 +381,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
       xl[half * 128 + r] = l;
       pair_sync();
       l += xl[(half ^ 1) * 128 + r];
+      if (a.sinks) l += ex2(a.sinks[kh * G + (r0 + r) % G] * 1.4426950408889634f - m_used);     // both halves hold the same m_used
       const float inv = l > 0.0f ? 1.0f / l : 0.0f;
       // this thread's half of the accumulator row: all loads under way at once, one wait
       uint32_t o[HD / 2];
@@ -686,6 +688,7 @@ attn_tc_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       xl[part * 128] = l;
       row_sync();
       l = (xl[0] + xl[128]) + (xl[256] + xl[384]);
+      if (a.sinks) l += ex2(a.sinks[kh * G + (r0 + r) % G] * 1.4426950408889634f - m_used);
       const float inv = l > 0.0f ? 1.0f / l : 0.0f;
       uint32_t o[HD / 4];      // this thread's quarter of the accumulator row
 #pragma unroll
@@ -781,7 +784,7 @@ extern "C" int slb_attention_tc(const void* q, const void* k_pool, const void* v
                                 const int* past, const int* counts, const int* block_table, int table_stride,
                                 int n_seqs, int max_count, long long tokens, long long pool_pages, int heads,
                                 int kv_heads, int head_dim, int window, float scale, int* status, int wide,
-                                int max_keys, void* stream) {
+                                int max_keys, const float* sinks, void* stream) {
   SLB_REQUIRE(slb_attention_tc_supported(heads, kv_heads, head_dim),
               "attention (tcgen05): heads=%d kv_heads=%d head_dim=%d is not taken (head size 64 or 128, group size a divisor of 128)",
               heads, kv_heads, head_dim);
@@ -814,7 +817,7 @@ extern "C" int slb_attention_tc(const void* q, const void* k_pool, const void* v
   AttnTcArgs a;
   a.out = (__nv_bfloat16*)out; a.seq_start = seq_start; a.past = past; a.counts = counts; a.block_table = block_table;
   a.table_stride = table_stride; a.heads = heads; a.kv_heads = kv_heads; a.window = window;
-  a.scale_log2 = scale * 1.4426950408889634f; a.status = status;
+  a.scale_log2 = scale * 1.4426950408889634f; a.status = status; a.sinks = sinks;
   const bool use_wide = wide < 0 ? wide_pays(n_seqs, max_count, max_keys, heads, kv_heads, window) : wide != 0;
   return head_dim == 64 ? launch_attn_tc<64>(mq, mk, mv, a, n_seqs, max_count, use_wide, (cudaStream_t)stream)
                         : launch_attn_tc<128>(mq, mk, mv, a, n_seqs, max_count, use_wide, (cudaStream_t)stream);

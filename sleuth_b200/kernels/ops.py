@@ -259,10 +259,17 @@ def decode_splits(n_seqs: int, kv_heads: int, group: int, table_stride: int, sms
     return three_buffers
 
 
+def _sinks_ok(sinks, heads: int) -> None:
+    _need(sinks is None or (sinks.is_cuda and sinks.dtype == torch.float32 and sinks.numel() == heads and sinks.is_contiguous()),
+          "attention: sinks are float32, one per head")
+
+
 def attention_prefill(q, k_pool, v_pool, out, seq_start, past, counts, block_table, max_count: int, heads: int,
-                      kv_heads: int, head_dim: int, window: int, scale: float, stream=None) -> None:
-    """Tensor-core attention for a step in which sequences bring any number of tokens."""
+                      kv_heads: int, head_dim: int, window: int, scale: float, stream=None, sinks=None) -> None:
+    """Tensor-core attention for a step in which sequences bring any number of tokens. ``sinks`` [heads]: a learned
+    score per head in the softmax denominator (as in ``attention``)."""
     _cuda(q, k_pool, v_pool, out, seq_start, past, counts, block_table)
+    _sinks_ok(sinks, heads)
     T, n = q.shape[0], block_table.shape[0]
     _need(q.shape == (T, heads, head_dim) and out.shape == (T, heads * head_dim), "attention: shapes disagree")
     _need(q.dtype == out.dtype == k_pool.dtype == v_pool.dtype == torch.bfloat16, "attention (tensor cores): bfloat16 only")
@@ -270,7 +277,7 @@ def attention_prefill(q, k_pool, v_pool, out, seq_start, past, counts, block_tab
     _need(seq_start.numel() >= n + 1 and past.numel() >= n and counts.numel() >= n, "attention: per-sequence tables")
     lib().call("slb_attention_prefill", _p(q), _p(k_pool), _p(v_pool), _p(out), _p(seq_start), _p(past), _p(counts),
                _p(block_table), block_table.shape[1], n, int(max_count), heads, kv_heads, head_dim, int(window),
-               float(scale), stream if stream is not None else current_stream())
+               float(scale), _p(sinks), stream if stream is not None else current_stream())
 
 
 def attention_tc_supported(heads: int, kv_heads: int, head_dim: int, dtype: torch.dtype) -> bool:
@@ -292,12 +299,13 @@ def attention_tc_takes_two_pages(n_seqs: int, max_count: int, max_keys: int, hea
 
 def attention_tc(q, k_pool, v_pool, out, seq_start, past, counts, block_table, max_count: int, heads: int,
                  kv_heads: int, head_dim: int, window: int, scale: float, stream=None, wide: bool | None = None,
-                 max_keys: int = 0) -> None:
+                 max_keys: int = 0, sinks=None) -> None:
     """Attention for a step in which sequences bring many tokens, on the tcgen05 tensor cores (same contract as
     ``attention_prefill``). A bounded wait that gave up inside the kernel shows in ``tc_check``. ``wide``: the
     kernel that walks two pages a step (True), one page a step (False), or the library's choice from the step's
     shape; ``max_keys`` (the most keys a sequence has after this step, 0 = not known) helps that choice."""
     _cuda(q, k_pool, v_pool, out, seq_start, past, counts, block_table)
+    _sinks_ok(sinks, heads)
     T, n = q.shape[0], block_table.shape[0]
     _need(q.shape == (T, heads, head_dim) and out.shape == (T, heads * head_dim), "attention: shapes disagree")
     _need(q.dtype == out.dtype == k_pool.dtype == v_pool.dtype == torch.bfloat16, "attention (tcgen05): bfloat16 only")
@@ -308,12 +316,13 @@ def attention_tc(q, k_pool, v_pool, out, seq_start, past, counts, block_table, m
     lib().call("slb_attention_tc", _p(q), _p(k_pool), _p(v_pool), _p(out), _p(seq_start), _p(past), _p(counts),
                _p(block_table), block_table.shape[1], n, int(max_count), T, k_pool.shape[0], heads, kv_heads, head_dim,
                int(window), float(scale), _p(_tc_status(q.device)), -1 if wide is None else int(bool(wide)),
-               int(max_keys), stream if stream is not None else current_stream())
+               int(max_keys), _p(sinks), stream if stream is not None else current_stream())
 
 
 def attention_decode(q, k_pool, v_pool, out, seq_start, past, block_table, heads: int, kv_heads: int, head_dim: int,
                      window: int, scale: float, splits: int, scratch, stream=None, qkv=None, qkv_kv_heads: int = 0,
-                     bias=None, q_gain=None, k_gain=None, cos=None, sin=None, eps: float = 1e-6, next_read=None) -> None:
+                     bias=None, q_gain=None, k_gain=None, cos=None, sin=None, eps: float = 1e-6, next_read=None,
+                     sinks=None) -> None:
     """Tensor-core attention for a step in which every sequence brings one token (split-KV).
 
     With ``qkv`` (the raw fused projection ``[n, (heads + 2 * qkv_kv_heads) * head_dim]``) the kernel also does what
@@ -322,6 +331,7 @@ def attention_decode(q, k_pool, v_pool, out, seq_start, past, block_table, heads
     ``next_read``: a tensor that the kernel after this one reads and no kernel writes (a weight matrix); the blocks
     ask the L2 cache for it once their own pages are on their way."""
     _cuda(q, k_pool, v_pool, out, seq_start, past, block_table, scratch, qkv, bias, q_gain, k_gain, cos, sin)
+    _sinks_ok(sinks, heads)
     n = block_table.shape[0]
     _need(out.shape == (n, heads * head_dim) and out.dtype == k_pool.dtype == v_pool.dtype == torch.bfloat16,
           "attention (tensor cores): shapes disagree or not bfloat16")
@@ -340,7 +350,7 @@ def attention_decode(q, k_pool, v_pool, out, seq_start, past, block_table, heads
                int(splits), _p(scratch), 0 if scratch is None else scratch.numel(), _p(counters),
                0 if counters is None else counters.numel(), _p(qkv), int(qkv_kv_heads), _p(bias), _p(q_gain), _p(k_gain),
                _p(cos), _p(sin), float(eps), _p(next_read) if _nbytes(next_read) else None, _nbytes(next_read),
-               stream if stream is not None else current_stream())
+               _p(sinks), stream if stream is not None else current_stream())
 
 
 _COUNTERS: dict = {}

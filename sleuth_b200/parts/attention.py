@@ -112,7 +112,7 @@ class GQAAttention(Part):
     def _attend(self, q, y, b, view, table, ws):
         """Attention of the step's (post-processed) queries over the cache into ``y``; the kernel by dtype and step shape."""
         s = self.spec
-        flash = ops.flash_supported(s.head_dim, self.ctx.dtype) and self.value_dim == s.head_dim and self.sinks is None
+        flash = ops.flash_supported(s.head_dim, self.ctx.dtype) and self.value_dim == s.head_dim
         if not flash:
             ops.attention(q, view.k_pool, view.v_pool, y, b.tok_seq, b.tok_pos, table, s.heads, s.kv_heads,
                           s.head_dim, view.window, self.scale, b.stream, sinks=self.sinks, value_dim=self.value_dim)
@@ -121,13 +121,15 @@ class GQAAttention(Part):
             floats = ops.decode_scratch_floats(b.n, s.heads, s.head_dim, splits)
             scratch = ws.take((floats,), torch.float32) if floats else None
             ops.attention_decode(q, view.k_pool, view.v_pool, y, b.seq_start, b.past, table, s.heads, s.kv_heads,
-                                 s.head_dim, view.window, self.scale, splits, scratch, b.stream)
+                                 s.head_dim, view.window, self.scale, splits, scratch, b.stream, sinks=self.sinks,
+                                 next_read=self.o.weight)
         elif use_tc_attention(s.heads, s.kv_heads, s.head_dim, self.ctx.dtype, b.max_count, self.scale):
             ops.attention_tc(q, view.k_pool, view.v_pool, y, b.seq_start, b.past, b.counts, table, b.max_count,
-                             s.heads, s.kv_heads, s.head_dim, view.window, self.scale, b.stream, max_keys=b.max_len)
+                             s.heads, s.kv_heads, s.head_dim, view.window, self.scale, b.stream, max_keys=b.max_len,
+                             sinks=self.sinks)
         else:
             ops.attention_prefill(q, view.k_pool, view.v_pool, y, b.seq_start, b.past, b.counts, table, b.max_count,
-                                  s.heads, s.kv_heads, s.head_dim, view.window, self.scale, b.stream)
+                                  s.heads, s.kv_heads, s.head_dim, view.window, self.scale, b.stream, sinks=self.sinks)
 
     def lead_weight(self):
         return self.qkv.weight if self.qkv is not None else None
@@ -159,7 +161,7 @@ class GQAAttention(Part):
             self._forward_wide(h, x, b, view, table, cos, sin, rot, ws)
             ws.release(mark)
             return
-        flash = ops.flash_supported(s.head_dim, self.ctx.dtype) and self.sinks is None
+        flash = ops.flash_supported(s.head_dim, self.ctx.dtype)
         fused_post = (flash and rot in (0, s.head_dim) and b.max_count > 1 and (writes or s.reads_shared_kv)
                       and use_tc(T, self.qkv.out_features, self.qkv.in_features))
         if fused_post:
@@ -191,7 +193,7 @@ class GQAAttention(Part):
                                  s.head_dim, view.window, self.scale, splits, scratch, b.stream, qkv=qkv,
                                  qkv_kv_heads=kvh, bias=self.bias, q_gain=self.q_gain, k_gain=self.k_gain,
                                  cos=cos if rot else None, sin=sin if rot else None, eps=s.qk_norm_eps,
-                                 next_read=self.o.weight)
+                                 next_read=self.o.weight, sinks=self.sinks)
             self.o.forward(y, into=x, ws=ws, stream=b.stream, next_read=getattr(b, "next_read", None))
             ws.release(mark)
             return

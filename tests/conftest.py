@@ -58,6 +58,22 @@ def lezepel_folders(tmp_path_factory):
     return out
 
 
+@pytest.fixture(scope="session")
+def rabadra_folders(tmp_path_factory):
+    """Model folders of the tiny Rabadra configurations, float32 weights, made once per session."""
+    import torch
+
+    import tiny_rabadra
+    from sleuth_b200.weights.random_init import write_random_model
+    out = {}
+    for name, cfg in tiny_rabadra.CONFIGS.items():
+        d = tmp_path_factory.mktemp(f"rabadra_{name}")
+        write_random_model(d, cfg, seed=tiny_rabadra.SEEDS[name], dtype=torch.float32, std=tiny_rabadra.STD)
+        tiny_rabadra.sharpen(d)
+        out[name] = str(d)
+    return out
+
+
 def pytest_terminal_summary(terminalreporter):
     """The largest differences from the plain implementation that the GPU tests saw (tests/closeness.py)."""
     import closeness

@@ -86,10 +86,12 @@ def clamped_expert(h, w, p, limit):
     return (g * torch.sigmoid(1.702 * g) * (u + 1.0)) @ w[p + "down"].T
 
 
-def route(h, w_router, r):
+def route(h, w_router, r, margins=None):
     """(chosen experts [T, top], their weights [T, top]): sigmoid scores; experts lie in ``groups.count`` equal
     groups of neighbours, a group scores the sum of its two largest scores, only the ``groups.keep`` best groups
-    may be chosen from; the ``top`` largest scores among those; weights = scores / (their sum + 1e-20) * scale."""
+    may be chosen from; the ``top`` largest scores among those; weights = scores / (their sum + 1e-20) * scale.
+    ``margins``: a list that receives, per token, by how much the choice was clear: the smaller of (last kept group's
+    score - best dropped group's) and (last chosen score - best score left out among the kept groups)."""
     n, top = r["experts"], r["top"]
     s = torch.sigmoid(h.to(torch.float32) @ w_router.to(torch.float32).T).to(h.dtype)
     groups = r.get("groups") or {"count": 1, "keep": 1}
@@ -100,14 +102,24 @@ def route(h, w_router, r):
     kept = group_score.topk(keep, dim=-1).indices
     open_groups = torch.zeros_like(group_score, dtype=torch.bool).scatter_(1, kept, True)
     allowed = open_groups[:, :, None].expand(-1, count, size).reshape(-1, n)
-    val, idx = torch.topk(s.masked_fill(~allowed, float("-inf")), top, dim=-1)
+    masked = s.masked_fill(~allowed, float("-inf"))
+    val, idx = torch.topk(masked, top, dim=-1)
     wt = val / (val.sum(dim=-1, keepdim=True) + 1e-20) * r["scale"]
+    if margins is not None:
+        clear = torch.full((s.shape[0],), float("inf"), dtype=s.dtype)
+        if keep < count:
+            g = group_score.sort(dim=-1, descending=True).values
+            clear = torch.minimum(clear, g[:, keep - 1] - g[:, keep])
+        if top < keep * size:
+            e = masked.sort(dim=-1, descending=True).values
+            clear = torch.minimum(clear, e[:, top - 1] - e[:, top])
+        margins.append(clear)
     return idx, wt
 
 
-def mixture(h, w, p, f):
+def mixture(h, w, p, f, margins=None):
     """Weighted sum of the chosen experts' outputs plus the shared expert's."""
-    idx, wt = route(h, w[p + "router"], f["router"])
+    idx, wt = route(h, w[p + "router"], f["router"], margins)
     out = torch.zeros(h.shape[0], w[p + "e0.down"].shape[0], dtype=h.dtype)
     for e in range(f["router"]["experts"]):
         share = (wt * (idx == e)).sum(dim=-1, keepdim=True)
@@ -117,7 +129,7 @@ def mixture(h, w, p, f):
     return out
 
 
-def layer(x, w, owner, L, eps):
+def layer(x, w, owner, L, eps, margins=None):
     """Parallel block with two norms: x + mixer(norm1 x) + ff(norm2 x); ``owner``: the layer whose tensors are used."""
     p = f"l{owner}."
     if L["type"] != "attention":
@@ -127,19 +139,20 @@ def layer(x, w, owner, L, eps):
     if f is not None:
         if f["kind"] != "moe":
             raise ValueError(f"unknown feed-forward {f['kind']!r}")
-        y = y + mixture(layer_norm(x, w[p + "norm2"], eps), w, p + "mlp.", f)
+        y = y + mixture(layer_norm(x, w[p + "norm2"], eps), w, p + "mlp.", f, margins)
     return x + y
 
 
-def forward(cfg, w, tokens, work=torch.float64, keep_stream=False):
-    """Logits [tokens, vocab] of one sequence (and, if asked, the stream after every layer)."""
+def forward(cfg, w, tokens, work=torch.float64, keep_stream=False, margins=None):
+    """Logits [tokens, vocab] of one sequence (and, if asked, the stream after every layer). ``margins``: a list that
+    receives one tensor [tokens] per routed layer: how clear each token's choice of experts was (``route``)."""
     w = {k: (v.to(work) if v.is_floating_point() else v) for k, v in w.items()}
     eps = cfg["norm"]["eps"]
     ids = torch.as_tensor(tokens, dtype=torch.long)
     x = layer_norm(w["embed"][ids], w["embed.norm"], eps)
     kept = []
     for i, L in enumerate(cfg["layers"]):
-        x = layer(x, w, L.get("weights_of", i), L, eps)
+        x = layer(x, w, L.get("weights_of", i), L, eps, margins)
         kept.append(x)
     logits = layer_norm(x, w["final.norm"], eps) @ w["head"].T
     cap = cfg.get("logit_softcap")

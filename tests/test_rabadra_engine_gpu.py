@@ -1,0 +1,243 @@
+"""The Rabadra model in the engine against the plain implementation, in float32 and bfloat16: whole prompts and the
+stream after every layer; prompts against token-by-token decoding; portions of several sizes down to two tokens;
+batches of unequal requests against each alone, batch after batch through a cache with room for one (slots and pages
+used again); the first tokens; long decoding across page borders; greedy generation through the entry point."""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+import tiny_rabadra as tr
+from closeness import check
+from plain import rabadra_plain as plain
+from plain.qwen3_plain import read_model
+
+pytestmark = pytest.mark.gpu
+
+# float32: the engine and the plain code differ by summation order only. bfloat16: weights are compared rounded
+# alike; activations and cache rows are rounded in the engine only, and where two router scores lie closer than that
+# rounding the engine may send a token to another expert than the plain code does, so a few rows may differ more:
+# bfloat16 asks that nine rows in ten (all but one of a few rows) lie inside the bound and that the others stay finite
+# and no larger than the logits themselves. float32 holds every row to its bound.
+TOL = {"fp32": dict(rtol=2e-4, atol=2e-4), "bf16": dict(rtol=0.0, atol=0.12)}
+NAMES = ["A", "B", "C", "D"]
+LENGTHS = {"A": [1, 7, 66, 150], "B": [3, 64, 65, 200], "C": [5, 130, 300], "D": [2, 129]}
+
+
+def load(folder, dtype, max_tokens=2048, **kw):
+    import sleuth_b200 as sb
+    return sb.load(folder, dtype=dtype, max_seq_len=1024, max_tokens=max_tokens, **kw)
+
+
+CLEAR = 0.01        # a choice of experts is clear when the scores at its edge differ by this much
+
+
+def oracle(folder, dtype):
+    cfg, w = read_model(folder)
+    if dtype == "bf16":
+        # matrices are narrowed on the device; gains, sinks and the router's matrix stay in float32 there
+        w = {k: (v.to(torch.bfloat16).float() if v.is_floating_point() and v.dim() > 1 and not k.endswith(".router") else v)
+             for k, v in w.items()}
+    cache = {}
+
+    def f(ids):
+        key = tuple(ids)
+        if key not in cache:
+            cache[key] = plain.forward(cfg, w, list(ids), torch.float64).float()
+        return cache[key]
+
+    def clearness(ids):
+        """The smallest margin with which any token of ``ids`` in any layer chose its experts."""
+        margins = []
+        cache[tuple(ids)] = plain.forward(cfg, w, list(ids), torch.float64, margins=margins).float()
+        return min((float(m.min()) for m in margins), default=float("inf"))
+    f.clearness = clearness
+    return f
+
+
+def close(got, want, dtype, label):
+    got, want = got.float().cpu(), want.float().cpu()
+    if dtype == "fp32":
+        return check(got, want, TOL[dtype], label)
+    worst = (got - want).abs().amax(dim=-1)
+    inside = worst <= TOL[dtype]["atol"]
+    allowed = max(1, len(worst) // 10)
+    assert int((~inside).sum()) <= allowed and float(worst.max()) <= float(want.abs().max()), \
+        f"{label}: {int((~inside).sum())} of {len(worst)} rows outside {TOL[dtype]['atol']}, worst {float(worst.max()):.3g}"
+    check(got[inside], want[inside], TOL[dtype], label)
+
+
+def requests_for(name, lengths, seed=0, ref=None):
+    """Random prompts. With ``ref`` (an oracle): prompts in which every token chooses its experts clearly. A run in
+    bfloat16 rounds the router's input, and where two scores lie closer than that rounding it may send a token to
+    another expert than the plain code does, which changes that token's row and, through attention, later ones; such a
+    close call says nothing about the engine, so the tests draw prompts until one has none (at most 40 draws; the
+    clearest one otherwise, and the comparison then allows for a few rows)."""
+    rng = np.random.default_rng(seed + tr.SEEDS[name])
+    out = []
+    for n in lengths:
+        best, best_clear = None, -1.0
+        for _ in range(40 if ref is not None else 1):
+            ids = rng.integers(0, tr.CONFIGS[name]["vocab"], size=n).tolist()
+            clear = ref.clearness(ids) if ref is not None else 0.0
+            if clear > best_clear:
+                best, best_clear = ids, clear
+            if clear >= CLEAR:
+                break
+        out.append(best)
+    return out
+
+
+@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
+@pytest.mark.parametrize("name", NAMES)
+def test_whole_prompts_and_the_stream_after_every_layer(name, dtype, rabadra_folders):
+    eng, ref = load(rabadra_folders[name], dtype), oracle(rabadra_folders[name], dtype)
+    for ids in requests_for(name, LENGTHS[name], ref=ref):
+        (slot,) = eng.open(1)
+        got = eng.step([(slot, ids, tuple(range(len(ids))))]).cpu()
+        eng.close([slot])
+        close(got, ref(ids), dtype, "rabadra " + dtype)
+    if dtype == "fp32":
+        cfg, w = read_model(rabadra_folders[name])
+        ids = requests_for(name, [21])[0]
+        _, stream = plain.forward(cfg, w, ids, torch.float64, keep_stream=True)
+        seen = []
+        eng.model.observe = lambda i, x: seen.append(x.detach().cpu().clone())
+        (slot,) = eng.open(1)
+        eng.step([(slot, ids, (0,))])
+        eng.close([slot])
+        eng.model.observe = None
+        assert len(seen) == stream.shape[0] == len(cfg["layers"])
+        for i, x in enumerate(seen):
+            torch.testing.assert_close(x.double(), stream[i], rtol=1e-4, atol=1e-4 * float(stream[i].abs().max()))
+
+
+@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
+@pytest.mark.parametrize("name", NAMES)
+def test_prompt_then_token_by_token(name, dtype, rabadra_folders):
+    eng, ref = load(rabadra_folders[name], dtype), oracle(rabadra_folders[name], dtype)
+    for ids in requests_for(name, [n for n in LENGTHS[name] if n > 40] + [34, 9], seed=1, ref=ref):
+        cut = max(1, len(ids) - 33)
+        (slot,) = eng.open(1)
+        rows = [eng.step([(slot, ids[:cut], (cut - 1,))]).cpu()]
+        for t in ids[cut:]:
+            rows.append(eng.step([(slot, [t], (0,))]).cpu().clone())
+        eng.close([slot])
+        close(torch.cat(rows), ref(ids)[cut - 1:], dtype, "rabadra " + dtype)
+
+
+@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
+@pytest.mark.parametrize("name", NAMES)
+def test_from_the_first_token_on_one_by_one(name, dtype, rabadra_folders):
+    eng, ref = load(rabadra_folders[name], dtype), oracle(rabadra_folders[name], dtype)
+    ids = requests_for(name, [70], seed=2, ref=ref)[0]
+    (slot,) = eng.open(1)
+    rows = [eng.step([(slot, [t], (0,))]).cpu().clone() for t in ids]
+    eng.close([slot])
+    close(torch.cat(rows), ref(ids), dtype, "rabadra " + dtype)
+
+
+@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
+@pytest.mark.parametrize("name", NAMES)
+@pytest.mark.parametrize("portion", [2, 7, 64, 100])
+def test_portions_of_a_prompt(name, portion, dtype, rabadra_folders):
+    eng, ref = load(rabadra_folders[name], dtype), oracle(rabadra_folders[name], dtype)
+    ids = requests_for(name, [131], seed=3, ref=ref)[0]
+    (slot,) = eng.open(1)
+    rows = []
+    for a in range(0, len(ids), portion):
+        part = ids[a:a + portion]
+        rows.append(eng.step([(slot, part, tuple(range(len(part))))]).cpu().clone())
+    eng.close([slot])
+    close(torch.cat(rows), ref(ids), dtype, "rabadra " + dtype)
+    if dtype == "fp32":         # and through the stepper's own cutting of long steps
+        small = load(rabadra_folders[name], dtype, max_step_tokens=portion + 1)
+        (slot,) = small.open(1)
+        got = small.step([(slot, ids, tuple(range(len(ids))))]).cpu()
+        close(got, ref(ids), dtype, "rabadra " + dtype)
+
+
+@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
+@pytest.mark.parametrize("name", NAMES)
+def test_unequal_batches_one_after_another_reuse_slots_and_pages(name, dtype, rabadra_folders):
+    """Three batches through a cache with room for one. Prompts and numbers of decoded tokens are unequal, the
+    shorter requests end earlier, and the next batch gets slots and pages still full of the last one's rows."""
+    eng, ref = load(rabadra_folders[name], dtype, max_tokens=64 * 8), oracle(rabadra_folders[name], dtype)
+    plans = [[(100, 20), (60, 3), (5, 27)], [(1, 12), (64, 1), (63, 2), (30, 30)], [(190, 9), (2, 40)]]
+    for b, plan in enumerate(plans):
+        reqs = requests_for(name, [p + d for p, d in plan], seed=10 + b, ref=ref)
+        slots = eng.open(len(reqs))
+        got = {i: [] for i in range(len(reqs))}
+        out = eng.step([(s, ids[:p], (p - 1,)) for s, ids, (p, d) in zip(slots, reqs, plan)]).cpu()
+        for i in range(len(reqs)):
+            got[i].append(out[i])
+        live, k = list(range(len(reqs))), 0
+        while live:
+            out = eng.step([(slots[i], [reqs[i][plan[i][0] + k]], (0,)) for i in live]).cpu()
+            for j, i in enumerate(live):
+                got[i].append(out[j].clone())
+            k += 1
+            done = [i for i in live if k >= plan[i][1]]
+            eng.close([slots[i] for i in done])
+            live = [i for i in live if i not in done]
+        for i, (ids, (p, d)) in enumerate(zip(reqs, plan)):
+            close(torch.stack(got[i]), ref(ids)[p - 1:], dtype, "rabadra " + dtype)
+        assert eng.cache.book.pages_in_use() == [0] * eng.cache.n_groups
+
+
+@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
+@pytest.mark.parametrize("name", ["A", "C"])
+def test_long_decoding_across_page_borders(name, dtype, rabadra_folders):
+    eng, ref = load(rabadra_folders[name], dtype), oracle(rabadra_folders[name], dtype)
+    ids = requests_for(name, [330], seed=4, ref=ref)[0]
+    (slot,) = eng.open(1)
+    rows = [eng.step([(slot, ids[:60], (59,))]).cpu()]
+    for t in ids[60:]:
+        rows.append(eng.step([(slot, [t], (0,))]).cpu().clone())
+    close(torch.cat(rows), ref(ids)[59:], dtype, "rabadra " + dtype)
+
+
+def test_float32_does_not_depend_on_the_batch_or_the_cut(rabadra_folders):
+    eng = load(rabadra_folders["B"], "fp32")
+    reqs = requests_for("B", [90, 3, 41], seed=5)
+    alone = []
+    for ids in reqs:
+        (slot,) = eng.open(1)
+        alone.append(eng.step([(slot, ids, (len(ids) - 1,))]).cpu().clone())
+        eng.close([slot])
+    slots = eng.open(3)
+    together = eng.step([(s, ids, (len(ids) - 1,)) for s, ids in zip(slots, reqs)]).cpu()
+    eng.close(slots)
+    torch.testing.assert_close(together, torch.cat(alone), rtol=1e-5, atol=1e-5)
+    (slot,) = eng.open(1)
+    eng.step([(slot, reqs[0][:37], ())])
+    cut = eng.step([(slot, reqs[0][37:], (len(reqs[0]) - 38,))]).cpu()
+    torch.testing.assert_close(cut, alone[0], rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("dtype", ["fp32", "bf16"])
+@pytest.mark.parametrize("name", ["A", "C"])
+def test_greedy_generation_through_the_entry_point(name, dtype, rabadra_folders):
+    """Unequal prompts through ``Engine.generate`` (its loop, its device-fed decode steps, its sampler) against greedy
+    decoding with the plain implementation, which follows the engine's tokens: at every step the engine's token must
+    be the plain code's best, or, where its two best logits lie closer than the run's rounding, one of those two."""
+    import sleuth_b200 as sb
+    eng, ref = load(rabadra_folders[name], dtype), oracle(rabadra_folders[name], dtype)
+    prompts = requests_for(name, [3, 70, 20, 1, 9, 130], seed=6, ref=ref)
+    out = eng.generate(prompts, max_new_tokens=12, sampling=sb.SamplingConfig(temperature=0), stop_ids=())
+    margin = {"fp32": 1e-3, "bf16": 0.3}[dtype]
+    clear = 0
+    for ids, r in zip(prompts, out):
+        assert len(r.new_ids) == 12
+        seq = list(ids)
+        for tok in r.new_ids:
+            top2 = torch.topk(ref(seq)[-1], 2)
+            if float(top2.values[0] - top2.values[1]) >= margin:
+                assert tok == int(top2.indices[0])
+                clear += 1
+            else:
+                assert tok in top2.indices.tolist()
+            seq.append(tok)
+    assert clear >= {"fp32": 60, "bf16": 12}[dtype]
