@@ -537,6 +537,15 @@ def lezepel_config(width, layers, heads, dim, rot, vdim, q_rank, kv_rank, expert
             "layers": block, "loop": {"start": 1, "stop": 2, "times": 1}}
 
 
+def rabadra_config(width, layers, heads, kv_heads, dim, rot, experts, top, ff, groups, keep, shared_ff, vocab=32768) -> dict:
+    mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "rot": {"base": 10000.0, "dims": rot}}
+    moe = {"kind": "moe", "expert": {"ff": ff, "limit": 7.0},
+           "router": {"experts": experts, "top": top, "scale": 1.0, "groups": {"count": groups, "keep": keep}},
+           "shared": {"ff": shared_ff, "limit": 7.0}}
+    return {"architecture": "Rabadra", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "logit_softcap": 30.0,
+            "layers": [{"type": "attention", "mixer": mixer, "mlp": moe} for _ in range(layers)]}
+
+
 def qwen3_like(width, layers, heads, head_dim, inter, vocab=32768) -> dict:
     return dict(CONFIG, vocab_size=vocab, hidden_size=width, num_hidden_layers=layers, num_attention_heads=heads,
                 num_key_value_heads=max(1, heads // 2), head_dim=head_dim, intermediate_size=inter, tie_word_embeddings=False)
@@ -551,6 +560,17 @@ DESIGN_SIZES = {
     "w2048": (dict(width=2048, layers=6, heads=16, dim=128, rot=64, vdim=128, q_rank=768, kv_rank=512, experts=64, top=6, ff=1408),
               dict(width=2048, layers=6, heads=16, head_dim=128, inter=8448)),
 }
+
+
+# Rabadra beside the same decoder: equal width, depth, heads (half as many key/value heads as query heads in both) and
+# a feed-forward as wide as the experts a token uses plus the shared one.
+RABADRA_SIZES = {
+    "w1024": (dict(width=1024, layers=8, heads=16, kv_heads=8, dim=64, rot=32, experts=16, top=4, ff=768, groups=4, keep=2, shared_ff=768),
+              dict(width=1024, layers=8, heads=16, head_dim=64, inter=3840)),
+    "w2048": (dict(width=2048, layers=6, heads=16, kv_heads=8, dim=128, rot=64, experts=32, top=4, ff=1024, groups=8, keep=4, shared_ff=1024),
+              dict(width=2048, layers=6, heads=16, head_dim=128, inter=5120)),
+}
+DESIGNS = {"lezepel": (lezepel_config, DESIGN_SIZES), "rabadra": (rabadra_config, RABADRA_SIZES)}
 
 
 def design_point(config: dict, prompt_len: int, batches, steps: int, warmup: int) -> dict:
@@ -612,15 +632,16 @@ def design_point(config: dict, prompt_len: int, batches, steps: int, warmup: int
 
 
 def run_design(args) -> dict:
-    """``--design lezepel``: the Lezepel design beside the closest existing model (the Qwen3 dense decoder) at equal
-    width, depth and active feed-forward width, random weights, bfloat16: prompt and decode throughput and where the
-    time goes. The default workload of this file does not change."""
+    """``--design lezepel`` / ``--design rabadra``: that design beside the closest existing model (the Qwen3 dense
+    decoder) at equal width, depth and active feed-forward width, random weights, bfloat16: prompt and decode throughput
+    and where the time goes. The default workload of this file does not change."""
     out = {"design": args.design, "dtype": "bf16", "data": "synthetic", "prompt": args.design_prompt, "sizes": {}}
-    for name, (mine, theirs) in DESIGN_SIZES.items():
+    make, sizes = DESIGNS[args.design]
+    for name, (mine, theirs) in sizes.items():
         if args.design_size not in ("all", name):
             continue
         out["sizes"][name] = {
-            "lezepel": design_point(lezepel_config(**mine), args.design_prompt, (1, 8), args.design_steps, max(3, args.warmup)),
+            args.design: design_point(make(**mine), args.design_prompt, (1, 8), args.design_steps, max(3, args.warmup)),
             "qwen3": design_point(qwen3_like(**theirs), args.design_prompt, (1, 8), args.design_steps, max(3, args.warmup)),
         }
     return out
@@ -640,7 +661,7 @@ def main() -> int:
     ap.add_argument("--skip-other-configs", action="store_true",
                     help="leave out the 32-bit block and the 4B- and 8B-shaped points (a quicker run)")
     ap.add_argument("--layers5", type=int, default=0, help="layers of the 8B-shaped point (0 = all 36)")
-    ap.add_argument("--design", choices=["lezepel"], default=None,
+    ap.add_argument("--design", choices=["lezepel", "rabadra"], default=None,
                     help="instead of the default workload: this design beside the closest existing model at equal size")
     ap.add_argument("--design-size", default="all", help="one of the sizes of --design (w1024, w2048) or all")
     ap.add_argument("--design-prompt", type=int, default=2048)

@@ -33,6 +33,7 @@ struct SkinnyArgs {
   int M, N, K, ldc;         // kSwiglu: N = inter (features of the output)
   NextRead next;            // what the kernel after this one reads, or nothing
   NextPages pages;          // cache pages that the attention kernel after this one reads first, or nothing
+  GateAct gate;             // kSwiglu: which gated activation joins a gate value and its up value (common.cuh)
 };
 
 __device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -241,7 +242,7 @@ __global__ void __launch_bounds__(kSkinnyWarps * 32, (MODE != kSwiglu && NF == 1
       float u = 0.0f;
 #pragma unroll
       for (int w8 = 0; w8 < kSkinnyWarps; ++w8) u += red[w8][NF + f][r][cc];
-      v = (v / (1.0f + expf(-v))) * u;
+      v = gated(a.gate, v, u);
       reinterpret_cast<__nv_bfloat16*>(a.C)[(size_t)r * a.ldc + feat] = __float2bfloat16_rn(v);
     } else if (MODE == kStoreBf16) {
       reinterpret_cast<__nv_bfloat16*>(a.C)[(size_t)r * a.ldc + feat] = __float2bfloat16_rn(v);
@@ -332,14 +333,31 @@ static int take_pages(SkinnyArgs& a, const NextPages* pages) {
   return 0;
 }
 
+static int skinny_run(const void* X, const void* W, void* C, int M, int N, int K, int ldc, int mode, GateAct gate,
+                      const void* next, long long next_bytes, const NextPages* pages, int features, void* stream);
+
 extern "C" int slb_gemm_skinny(const void* X, const void* W, void* C, int M, int N, int K, int ldc, int mode,
                                const void* next, long long next_bytes, const NextPages* pages, int features, void* stream) {
+  return skinny_run(X, W, C, M, N, K, ldc, mode, GateAct{kGateSilu, 0.0f, 1.0f}, next, next_bytes, pages, features, stream);
+}
+
+// The gated form (mode 3) with another activation than SiLU: kind, limit, alpha as in common.cuh.
+extern "C" int slb_gemm_skinny_gated(const void* X, const void* W, void* C, int M, int N, int K, int ldc, int kind,
+                                     float limit, float alpha, const void* next, long long next_bytes,
+                                     const NextPages* pages, int features, void* stream) {
+  SLB_REQUIRE(kind >= kGateSilu && kind <= kGateClampedSwish, "gemm_skinny: unknown activation %d", kind);
+  return skinny_run(X, W, C, M, N, K, ldc, kSwiglu, GateAct{kind, limit, alpha}, next, next_bytes, pages, features, stream);
+}
+
+static int skinny_run(const void* X, const void* W, void* C, int M, int N, int K, int ldc, int mode, GateAct gate,
+                      const void* next, long long next_bytes, const NextPages* pages, int features, void* stream) {
   SLB_REQUIRE(slb_gemm_skinny_supported(M, N, K),
               "gemm_skinny: M=%d N=%d K=%d is outside what the kernel takes (1 <= M <= 64, K a multiple of 32)", M, N, K);
   SLB_REQUIRE(mode >= 0 && mode <= 3 && ldc >= N, "gemm_skinny: mode=%d ldc=%d N=%d", mode, ldc, N);
   SLB_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_skinny: X and W must be 16-byte aligned");
   SkinnyArgs a{};
   a.X = (const __nv_bfloat16*)X; a.W = (const __nv_bfloat16*)W; a.C = C; a.M = M; a.N = N; a.K = K; a.ldc = ldc;
+  a.gate = gate;
   SLB_REQUIRE(next_bytes >= 0 && (uintptr_t)next % 16 == 0, "gemm_skinny: the range to prefetch must be 16-byte aligned");
   a.next.ptr = (const char*)next; a.next.bytes = next ? next_bytes : 0;
   if (int rc = take_pages(a, pages)) return rc;
@@ -360,6 +378,7 @@ extern "C" int slb_gemm_skinny_norm(const float* X, const float* gain, float eps
               "gemm_skinny: X, gain and W must be 16-byte aligned");
   SkinnyArgs a{};
   a.Xf = X; a.gain = gain; a.eps = eps; a.W = (const __nv_bfloat16*)W; a.C = C; a.M = M; a.N = N; a.K = K; a.ldc = ldc;
+  a.gate = GateAct{kGateSilu, 0.0f, 1.0f};
   SLB_REQUIRE(next_bytes >= 0 && (uintptr_t)next % 16 == 0, "gemm_skinny: the range to prefetch must be 16-byte aligned");
   a.next.ptr = (const char*)next; a.next.bytes = next ? next_bytes : 0;
   if (int rc = take_pages(a, pages)) return rc;

@@ -49,6 +49,7 @@ struct TcArgs {
   // Null: the plain product.
   const int* group_tiles;
   int group_w_rows;
+  GateAct gate;         // kTcSwiglu: which gated activation joins a gate value and its up value (common.cuh)
 };
 
 // Where a tile lies: first row, one past the last row it may store, first row of its weights in W.
@@ -213,6 +214,13 @@ __device__ __forceinline__ void qkv_head_epilogue(const TcQkv& q, uint32_t taddr
 }
 
 __device__ __forceinline__ float fast_silu(float g) { return __fdividef(g, 1.0f + __expf(-g)); }
+// The other gated activations with the same fast exponential and division.
+__device__ __forceinline__ float fast_gated(const GateAct& f, float g, float u) {
+  if (f.kind == kGateRelu) return fmaxf(g, 0.0f) * u;
+  g = fminf(g, f.limit);
+  u = fminf(fmaxf(u, -f.limit), f.limit);
+  return __fdividef(g, 1.0f + __expf(-f.alpha * g)) * (u + 1.0f);
+}
 
 // Stores 32 consecutive float32 accumulator values of one row according to the mode.
 __device__ __forceinline__ void store_row32(const TcArgs& a, int row, int col0, const float (&v)[32]) {
@@ -511,7 +519,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
           uint32_t u[32];
           tmem_ld32(lane_base + BN / 2 + c, u);
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = fast_silu(__uint_as_float(r[j])) * __uint_as_float(u[j]);
+          for (int j = 0; j < 32; ++j)
+            v[j] = a.gate.kind == kGateSilu ? fast_silu(__uint_as_float(r[j])) * __uint_as_float(u[j])
+                                            : fast_gated(a.gate, __uint_as_float(r[j]), __uint_as_float(u[j]));
         } else {
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
@@ -642,8 +652,23 @@ extern "C" int slb_gemm_tc_supported(int M, int N, int K) { return M >= 1 && N >
 // mode: 0 store bfloat16, 1 store float32, 2 add into float32, 3 gated activation (W holds N gate rows then N up
 // rows; C is [M, N] bfloat16). `status` is a device int that the caller zeroed; the kernel writes a non-zero code
 // there if one of its bounded waits gave up (the result is then invalid and the caller must say so).
+static int gemm_tc_run(const void* X, const void* W, void* C, int M, int N, int K, int ldc, int mode, GateAct gate,
+                       int* status, void* stream);
+
 extern "C" int slb_gemm_tc(const void* X, const void* W, void* C, int M, int N, int K, int ldc, int mode, int* status,
                            void* stream) {
+  return gemm_tc_run(X, W, C, M, N, K, ldc, mode, GateAct{kGateSilu, 0.0f, 1.0f}, status, stream);
+}
+
+// The gated form (mode 3) with another activation than SiLU: kind, limit, alpha as in common.cuh.
+extern "C" int slb_gemm_tc_gated(const void* X, const void* W, void* C, int M, int N, int K, int ldc, int kind, float limit,
+                                 float alpha, int* status, void* stream) {
+  SLB_REQUIRE(kind >= kGateSilu && kind <= kGateClampedSwish, "gemm_tc: unknown activation %d", kind);
+  return gemm_tc_run(X, W, C, M, N, K, ldc, kTcSwiglu, GateAct{kind, limit, alpha}, status, stream);
+}
+
+static int gemm_tc_run(const void* X, const void* W, void* C, int M, int N, int K, int ldc, int mode, GateAct gate,
+                       int* status, void* stream) {
   SLB_REQUIRE(slb_gemm_tc_supported(M, N, K), "gemm_tc: M=%d N=%d K=%d is not taken (K must be a multiple of 8)", M, N, K);
   SLB_REQUIRE(mode >= 0 && mode <= 3 && ldc >= N && status != nullptr, "gemm_tc: mode=%d ldc=%d N=%d", mode, ldc, N);
   SLB_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0) && ((uintptr_t)C % 16 == 0),
@@ -669,7 +694,7 @@ extern "C" int slb_gemm_tc(const void* X, const void* W, void* C, int M, int N, 
   if (rc) return rc;
   TcArgs a;
   a.C = C; a.M = M; a.N = N; a.K = K; a.ldc = ldc; a.mode = mode; a.up_row0 = N; a.status = status;
-  a.group_tiles = nullptr; a.group_w_rows = 0;
+  a.group_tiles = nullptr; a.group_w_rows = 0; a.gate = gate;
   cudaStream_t s = (cudaStream_t)stream;
   if (pair) return bn == 256 ? launch_tc<256, false, true>(mx, mw, a, s) : launch_tc<128, false, true>(mx, mw, a, s);
   switch (bn) {
@@ -684,8 +709,20 @@ extern "C" int slb_gemm_tc(const void* X, const void* W, void* C, int M, int N, 
 // kernel in front: [0] = their number, then (group, first row, rows) each; at most `max_row_tiles` of them), W stacks
 // the groups' matrices (`w_rows` rows each: N, or 2 N for the gated form: gate rows then up rows), C [M, N] gets
 // each row's product with its own group's matrix. mode: 0 bfloat16, 1 float32, 3 gated activation.
+extern "C" int slb_gemm_tc_grouped_gated(const void* X, const void* W, void* C, int M, int N, int K, int groups, int mode,
+                                         const int* group_tiles, int max_row_tiles, int kind, float limit, float alpha,
+                                         int* status, void* stream);
+
 extern "C" int slb_gemm_tc_grouped(const void* X, const void* W, void* C, int M, int N, int K, int groups, int mode,
                                    const int* group_tiles, int max_row_tiles, int* status, void* stream) {
+  return slb_gemm_tc_grouped_gated(X, W, C, M, N, K, groups, mode, group_tiles, max_row_tiles, kGateSilu, 0.0f, 1.0f, status, stream);
+}
+
+// The same with the gated activation of mode 3 named: kind, limit, alpha as in common.cuh.
+extern "C" int slb_gemm_tc_grouped_gated(const void* X, const void* W, void* C, int M, int N, int K, int groups, int mode,
+                                         const int* group_tiles, int max_row_tiles, int kind, float limit, float alpha,
+                                         int* status, void* stream) {
+  SLB_REQUIRE(kind >= kGateSilu && kind <= kGateClampedSwish, "gemm_tc_grouped: unknown activation %d", kind);
   SLB_REQUIRE(slb_gemm_tc_supported(M, N, K) && groups >= 1, "gemm_tc_grouped: M=%d N=%d K=%d groups=%d", M, N, K, groups);
   SLB_REQUIRE((mode == 0 || mode == 1 || mode == 3) && status != nullptr && group_tiles != nullptr && max_row_tiles >= 1,
               "gemm_tc_grouped: mode=%d", mode);
@@ -701,7 +738,7 @@ extern "C" int slb_gemm_tc_grouped(const void* X, const void* W, void* C, int M,
   if (rc) return rc;
   TcArgs a;
   a.C = C; a.N = N; a.K = K; a.ldc = N; a.mode = mode; a.up_row0 = N; a.status = status;
-  a.group_tiles = group_tiles; a.group_w_rows = w_rows;
+  a.group_tiles = group_tiles; a.group_w_rows = w_rows; a.gate = GateAct{kind, limit, alpha};
   a.M = max_row_tiles * kTcBM;                          // sizes the grid; the kernel reads the true number of row tiles
   (void)bn;
   return launch_tc<256>(mx, mw, a, (cudaStream_t)stream);
@@ -737,7 +774,7 @@ extern "C" int slb_gemm_tc_qkv(const void* X, const void* W, int M, int K, int h
   if (rc) return rc;
   TcArgs a;
   a.C = nullptr; a.M = M; a.N = N; a.K = K; a.ldc = N; a.mode = kTcQkv; a.up_row0 = N; a.status = status;
-  a.group_tiles = nullptr; a.group_w_rows = 0;
+  a.group_tiles = nullptr; a.group_w_rows = 0; a.gate = GateAct{kGateSilu, 0.0f, 1.0f};
   TcQkv qa;
   qa.bias = bias; qa.q_gain = q_gain; qa.k_gain = k_gain; qa.cos_table = cos_table; qa.sin_table = sin_table;
   qa.q_out = (__nv_bfloat16*)q_out; qa.k_pool = (__nv_bfloat16*)k_pool; qa.v_pool = (__nv_bfloat16*)v_pool;

@@ -629,15 +629,17 @@ __global__ void moe_combine_sorted_kernel(float* __restrict__ x, const float* __
 
 using namespace slb;
 
-extern "C" int slb_gemm_tc_grouped(const void* X, const void* W, void* C, int M, int N, int K, int groups, int mode,
-                                   const int* group_tiles, int max_row_tiles, int* status, void* stream);
+extern "C" int slb_gemm_tc_grouped_gated(const void* X, const void* W, void* C, int M, int N, int K, int groups, int mode,
+                                         const int* group_tiles, int max_row_tiles, int kind, float limit, float alpha,
+                                         int* status, void* stream);
 
-// The experts of a step of many pairs on the tcgen05 tensor cores (bfloat16, SiLU): the tokens' rows gathered into the
+// The experts of a step of many pairs on the tcgen05 tensor cores (bfloat16, any of the gated activations): the tokens' rows gathered into the
 // expert order (xs [pairs, dim]), the grouped product with the gated activation in its epilogue (act [pairs, ff]), the
 // grouped down product (y [pairs, dim] float32, expert order, unweighted), and the weighted sum into the stream.
 extern "C" int slb_moe_experts_tc(const void* h, const void* w_gu, const void* w_down, const int* list, const int* place,
                                   const float* weight, const int* tiles, void* xs, void* act, float* y, float* x, int tokens,
-                                  int dim, int ff, int E, int top, int* status, void* stream) {
+                                  int dim, int ff, int E, int top, int act_kind, float act_limit, float act_alpha,
+                                  int* status, void* stream) {
   SLB_REQUIRE(tokens > 0 && dim > 0 && ff > 0 && E > 0 && top > 0 && dim % 8 == 0 && ff % 8 == 0,
               "moe_experts_tc: tokens=%d dim=%d ff=%d experts=%d top=%d (inner sizes must be multiples of 8)", tokens, dim, ff, E, top);
   SLB_REQUIRE(tiles != nullptr && status != nullptr, "moe_experts_tc: the row tiles and the status word are needed");
@@ -649,9 +651,11 @@ extern "C" int slb_moe_experts_tc(const void* h, const void* w_gu, const void* w
          (int)pairs, dim, top);
   int rc = check_launch("moe_gather");
   if (rc) return rc;
-  rc = slb_gemm_tc_grouped(xs, w_gu, act, (int)pairs, ff, dim, E, 3, tiles, (int)max_tiles, status, stream);
+  rc = slb_gemm_tc_grouped_gated(xs, w_gu, act, (int)pairs, ff, dim, E, 3, tiles, (int)max_tiles, act_kind, act_limit, act_alpha,
+                                 status, stream);
   if (rc) return rc;
-  rc = slb_gemm_tc_grouped(act, w_down, y, (int)pairs, dim, ff, E, 1, tiles, (int)max_tiles, status, stream);
+  rc = slb_gemm_tc_grouped_gated(act, w_down, y, (int)pairs, dim, ff, E, 1, tiles, (int)max_tiles, kGateSilu, 0.0f, 1.0f, status,
+                                 stream);
   if (rc) return rc;
   const size_t total = (size_t)tokens * dim;
   size_t blocks = (total + 255) / 256;

@@ -160,7 +160,9 @@ _SIGNATURES = {
     "slb_latent_attention": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, I, P],
     "slb_latent_gate": [P, P, P, I, I, I, I, P],
     "slb_moe_route": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P],
-    "slb_moe_experts_tc": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, P, P],
+    "slb_moe_experts_tc": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, F, P, P],
+    "slb_gemm_skinny_gated": [P, P, P, I, I, I, I, I, F, F, P, L, P, I, P],
+    "slb_gemm_tc_gated": [P, P, P, I, I, I, I, I, F, F, P, P],
     "slb_moe_experts": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, F, I, P],
 }
 

@@ -436,8 +436,16 @@ def _pages_arg(pages):
     return None if pages is None else ctypes.addressof(pages)
 
 
+def _gate_args(gate) -> tuple | None:
+    """(kind number, limit, alpha) of a gated product's activation given as (name, limit, alpha); None = SiLU."""
+    if gate is None or gate[0] == "silu":
+        return None
+    _need(gate[0] in ACTIVATIONS, f"gated product: activation {gate[0]!r} is not one of {sorted(ACTIVATIONS)}")
+    return ACTIVATIONS[gate[0]], float(gate[1]), float(gate[2])
+
+
 def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: str, stream=None, next_read=None,
-                next_pages=None, features: int = 0) -> None:
+                next_pages=None, features: int = 0, gate=None) -> None:
     """out = x[M, K] @ w^T for M <= 16 (bfloat16 in, float32 accumulation). mode: "bf16" / "f32" store,
     "add" adds into a float32 ``out``, "swiglu" takes w = [gate rows; up rows] and stores silu(gate) * up.
     ``next_read``: a weight tensor that the kernel after this one reads; the blocks ask the L2 cache for it.
@@ -448,6 +456,11 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: str, 
     _need(x.dtype == w.dtype == torch.bfloat16 and w.shape[1] == K and out.shape[0] == M, "gemm_skinny: shapes or dtypes")
     _need(w.shape[0] == (2 * N if mode == "swiglu" else N), "gemm_skinny: weight rows")
     _need(out.dtype == (torch.bfloat16 if mode in ("bf16", "swiglu") else torch.float32), "gemm_skinny: output dtype")
+    g = _gate_args(gate) if mode == "swiglu" else None
+    if g is not None:       # ``gate`` = (name, limit, alpha): the gated form with another activation than SiLU
+        lib().call("slb_gemm_skinny_gated", _p(x), _p(w), _p(out), M, N, K, N, *g, _p(next_read) if _nbytes(next_read) else None,
+                   _nbytes(next_read), _pages_arg(next_pages), int(features), stream if stream is not None else current_stream())
+        return
     lib().call("slb_gemm_skinny", _p(x), _p(w), _p(out), M, N, K, N, SKINNY_MODES[mode], _p(next_read) if _nbytes(next_read) else None, _nbytes(next_read),
                _pages_arg(next_pages), int(features), stream if stream is not None else current_stream())
 
@@ -486,7 +499,7 @@ def _tc_status(device) -> torch.Tensor:
     return st
 
 
-def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: str, stream=None) -> None:
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: str, stream=None, gate=None) -> None:
     """out = x[M, K] @ w^T on the tcgen05 tensor cores (bfloat16 in, float32 accumulation in tensor memory).
     mode as for ``gemm_skinny``: "bf16" / "f32" store, "add" into a float32 ``out``, "swiglu" with w = [gate; up]."""
     _cuda(x, w, out)
@@ -495,6 +508,11 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: str, stre
     _need(x.dtype == w.dtype == torch.bfloat16 and w.shape[1] == K and out.shape[0] == M, "gemm_tc: shapes or dtypes")
     _need(w.shape[0] == (2 * N if mode == "swiglu" else N), "gemm_tc: weight rows")
     _need(out.dtype == (torch.bfloat16 if mode in ("bf16", "swiglu") else torch.float32), "gemm_tc: output dtype")
+    g = _gate_args(gate) if mode == "swiglu" else None
+    if g is not None:       # ``gate`` = (name, limit, alpha): the gated form with another activation than SiLU
+        lib().call("slb_gemm_tc_gated", _p(x), _p(w), _p(out), M, N, K, N, *g, _p(_tc_status(x.device)),
+                   stream if stream is not None else current_stream())
+        return
     lib().call("slb_gemm_tc", _p(x), _p(w), _p(out), M, N, K, N, SKINNY_MODES[mode], _p(_tc_status(x.device)),
                stream if stream is not None else current_stream())
 
@@ -913,8 +931,9 @@ def moe_experts(h, w_gate_up, w_down, counts, order, weight, act, y, x, top: int
                stream if stream is not None else current_stream())
 
 
-def moe_experts_tc(h, w_gate_up, w_down, order, place, weight, tiles, xs, act, y, x, top: int, stream=None) -> None:
-    """The same sum as ``moe_experts`` for steps of many pairs, bfloat16 and SiLU: the tokens' rows gathered into the
+def moe_experts_tc(h, w_gate_up, w_down, order, place, weight, tiles, xs, act, y, x, top: int, stream=None,
+                   activation: str = "silu", limit: float = 0.0, alpha: float = 1.0) -> None:
+    """The same sum as ``moe_experts`` for steps of many pairs in bfloat16: the tokens' rows gathered into the
     expert order (``xs`` [T * top, d]) and both products as grouped tcgen05 products over the row tiles that
     ``moe_route`` wrote into ``tiles``; ``y`` [T * top, d] float32 comes out in the expert order."""
     _cuda(h, w_gate_up, w_down, order, place, weight, tiles, xs, act, y, x)
@@ -929,5 +948,5 @@ def moe_experts_tc(h, w_gate_up, w_down, order, place, weight, tiles, xs, act, y
     _need(x.shape == (T, d) and x.dtype == torch.float32, "moe_experts_tc: the stream")
     _need(tiles.dtype == torch.int32 and tiles.numel() >= moe_tile_words(T, top, E), "moe_experts_tc: row-tile table")
     lib().call("slb_moe_experts_tc", _p(h), _p(w_gate_up), _p(w_down), _p(order), _p(place), _p(weight), _p(tiles), _p(xs),
-               _p(act), _p(y), _p(x), T, d, ff, E, int(top), _p(_tc_status(h.device)),
-               stream if stream is not None else current_stream())
+               _p(act), _p(y), _p(x), T, d, ff, E, int(top), ACTIVATIONS[activation], float(limit), float(alpha),
+               _p(_tc_status(h.device)), stream if stream is not None else current_stream())

@@ -28,7 +28,10 @@ class GatedMLP(Part):
             raise ValueError(f"gated_mlp: activation {spec.activation!r} is not supported ({sorted(ops.ACTIVATIONS)})")
         if spec.activation == "clamped_swish" and not spec.limit > 0:
             raise ValueError(f"gated_mlp: the clamped swish needs a positive limit, got {spec.limit}")
-        self.silu = spec.activation == "silu"     # the products' fused epilogues know this gate only
+        self.silu = spec.activation == "silu"
+        # the products' epilogues apply silu and the clamped swish themselves; relu runs as product + activation kernel
+        self.fused = spec.activation in ("silu", "clamped_swish")
+        self.gate = (spec.activation, spec.limit, spec.alpha)
         self.spec, self.ctx = spec, ctx
         self.gate_up = self.down = None
 
@@ -54,24 +57,25 @@ class GatedMLP(Part):
         T = h.shape[0]
         mark = ws.mark()
         act = ws.take((T, self.spec.intermediate), self.ctx.dtype)
-        if not self.silu:
+        if not self.fused:
             gu = self.gate_up.forward(h, ws=ws, stream=b.stream)
             ops.gated_act(gu, act, self.spec.activation, b.stream, self.spec.limit, self.spec.alpha)
         elif self.ctx.dtype == torch.bfloat16 and linear.use_skinny(T, self.spec.intermediate, self.spec.hidden):
             # norm in the product's prologue (when handed the stream), activation in its epilogue
-            if (isinstance(h, Normed) and h.gain is not None and FUSE_NORM
+            if (isinstance(h, Normed) and h.gain is not None and FUSE_NORM and self.silu
                     and ops.skinny_supported(T, self.spec.intermediate, self.spec.hidden, norm=True)):
                 ops.gemm_skinny_norm(h.x, h.gain, h.eps, self.gate_up.weight, act, "swiglu", b.stream, self.down.weight)
             else:
                 hh = h.tensor() if isinstance(h, Normed) else h
                 f = linear.tuned_features("swiglu", T, self.spec.intermediate, self.spec.hidden,
-                                          lambda f: ops.gemm_skinny(hh, self.gate_up.weight, act, "swiglu", b.stream, features=f))
-                ops.gemm_skinny(hh, self.gate_up.weight, act, "swiglu", b.stream, self.down.weight, features=f)
+                                          lambda f: ops.gemm_skinny(hh, self.gate_up.weight, act, "swiglu", b.stream, features=f,
+                                                                    gate=self.gate))
+                ops.gemm_skinny(hh, self.gate_up.weight, act, "swiglu", b.stream, self.down.weight, features=f, gate=self.gate)
         elif self.ctx.dtype == torch.bfloat16 and linear.use_tc(T, self.spec.intermediate, self.spec.hidden):
-            ops.gemm_tc(h.tensor() if isinstance(h, Normed) else h, self.gate_up.weight, act, "swiglu", b.stream)
+            ops.gemm_tc(h.tensor() if isinstance(h, Normed) else h, self.gate_up.weight, act, "swiglu", b.stream, gate=self.gate)
         else:
             gu = self.gate_up.forward(h, ws=ws, stream=b.stream)
-            ops.swiglu(gu, act, b.stream)
+            ops.gated_act(gu, act, self.spec.activation, b.stream, self.spec.limit, self.spec.alpha)
         self.down.forward(act, into=x, ws=ws, stream=b.stream, next_read=getattr(b, "next_read", None))
         ws.release(mark)
 

@@ -94,8 +94,8 @@ class RoutedExperts(Part):
         act = ws.take((pairs, s.intermediate), dt)
         y = ws.take((pairs, s.hidden), torch.float32)
         logits = ws.take((T, s.experts), torch.float32)
-        # steps of many pairs: the tcgen05 grouped products (bfloat16, SiLU, inner sizes that TMA takes)
-        grouped = (dt == torch.bfloat16 and s.activation == "silu" and pairs >= TC_PAIRS and s.hidden % 8 == 0
+        # steps of many pairs: the tcgen05 grouped products (bfloat16, inner sizes that TMA takes)
+        grouped = (dt == torch.bfloat16 and pairs >= TC_PAIRS and s.hidden % 8 == 0
                    and s.intermediate % 8 == 0)
         tiles = ws.take((ops.moe_tile_words(T, s.top, s.experts),), torch.int32) if grouped else None
         ops.moe_route(h, self.w_router, self.bias, choice, weight, rank, counts, place, order, s.top, b.stream, logits, tiles,
@@ -103,7 +103,8 @@ class RoutedExperts(Part):
                       scale=s.route_scale)
         if grouped:
             xs = ws.take((pairs, s.hidden), dt)
-            ops.moe_experts_tc(h, self.w_gate_up, self.w_down, order, place, weight, tiles, xs, act, y, x, s.top, b.stream)
+            ops.moe_experts_tc(h, self.w_gate_up, self.w_down, order, place, weight, tiles, xs, act, y, x, s.top, b.stream,
+                               activation=s.activation, limit=s.limit, alpha=s.alpha)
         else:
             ops.moe_experts(h, self.w_gate_up, self.w_down, counts, order, weight, act, y, x, s.top, s.activation, b.stream,
                             choice, place, limit=s.limit, alpha=s.alpha)

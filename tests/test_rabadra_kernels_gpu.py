@@ -259,9 +259,40 @@ def test_experts_with_the_clamped_swish(T, d, ff, E, top, count, keep, dtype):
     x = torch.zeros(T, d, dtype=torch.float32, device=DEV)
     o.moe_experts(h.to(DEV), w_gu, w_dn, counts, order, weight, act, y, x, top, "clamped_swish", choice=choice, place=place,
                   limit=1.25, alpha=1.702)
-    tol = TOL[dtype] if dtype == "fp32" else dict(rtol=3e-2, atol=3e-2)
     diff = (x.cpu().double() - want).abs().amax(dim=-1)
     if dtype == "fp32":
         torch.testing.assert_close(x.cpu().double(), want, rtol=1e-4, atol=1e-4)
     else:       # the activations are rounded once on the device; the choice is made from the same float32 logits
         assert float(diff.max()) <= 0.05 * max(1.0, float(want.abs().max()))
+    if dtype == "bf16" and d % 8 == 0 and ff % 8 == 0:      # and as grouped tensor-memory products over the experts' row tiles
+        tiles = torch.empty(o.moe_tile_words(T, top, E), dtype=torch.int32, device=DEV)
+        o.moe_route(h.to(DEV), w_r.to(DEV), None, choice, weight, rank, counts, place, order, top, logits=logits, tiles=tiles,
+                    scoring="sigmoid", groups=count, keep=keep, scale=1.75)
+        xs = torch.empty(pairs, d, dtype=dt, device=DEV)
+        x3 = torch.zeros(T, d, dtype=torch.float32, device=DEV)
+        o.moe_experts_tc(h.to(DEV), w_gu, w_dn, order, place, weight, tiles, xs, act, y, x3, top, activation="clamped_swish",
+                         limit=1.25, alpha=1.702)
+        o.gemm_tc_check(DEV)
+        diff = (x3.cpu().double() - want).abs().amax(dim=-1)
+        assert float(diff.max()) <= 0.05 * max(1.0, float(want.abs().max()))
+
+
+@pytest.mark.parametrize("T", [1, 8, 200])
+def test_gated_products_apply_the_clamped_swish_in_their_epilogue(T):
+    o = ops()
+    g = torch.Generator().manual_seed(T)
+    d, ff = 256, 192
+    h = torch.randn(T, d, generator=g).to(torch.bfloat16)
+    w = {"gate": (torch.randn(ff, d, generator=g) * 0.2).to(torch.bfloat16), "up": (torch.randn(ff, d, generator=g) * 0.2).to(torch.bfloat16),
+         "down": torch.eye(ff, dtype=torch.float64)}
+    want = plain.clamped_expert(h.double(), {k: v.double() for k, v in w.items()}, "", 1.5)
+    w_gu = torch.cat([w["gate"], w["up"]]).to(DEV).contiguous()
+    act = torch.empty(T, ff, dtype=torch.bfloat16, device=DEV)
+    gate = ("clamped_swish", 1.5, 1.702)
+    if T <= 32:
+        o.gemm_skinny(h.to(DEV), w_gu, act, "swiglu", gate=gate)
+    else:
+        o.gemm_tc(h.to(DEV), w_gu, act, "swiglu", gate=gate)
+        o.gemm_tc_check(DEV)
+    assert float((h.double() @ w["gate"].double().T).abs().max()) > 1.5
+    torch.testing.assert_close(act.cpu().double(), want, rtol=2e-2, atol=2e-2)
