@@ -179,6 +179,65 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const float* __res
   for (int i = threadIdx.x; i < dim; i += blockDim.x) o[i] = from_f32<TO>(((row[i] - mean) * inv) * w[i]);
 }
 
+// The same for widths that are multiples of 4 (16-byte loads, the row kept in registers between the passes), and for two
+// gains at once: two norms of the same rows that differ in their gains only (the two norms of a parallel layer) share the
+// mean and the variance, so one pass over the stream serves both; out2 null: one output.
+template <typename TO, int PER_THREAD>
+__global__ void layernorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ w, TO* __restrict__ out,
+                                     const float* __restrict__ w2, TO* __restrict__ out2, const int* __restrict__ rows,
+                                     int dim, float eps) {
+  pdl_enter();
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  const float4* xr = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * dim);
+  const int n4 = dim >> 2;
+  float4 v[PER_THREAD];
+  float sum = 0.0f;
+#pragma unroll
+  for (int i = 0; i < PER_THREAD; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    v[i] = c < n4 ? xr[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+    sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+  }
+  const float mean = block_sum(sum, scratch) / (float)dim;
+  float ss = 0.0f;
+#pragma unroll
+  for (int i = 0; i < PER_THREAD; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    if (c < n4) {
+      v[i].x -= mean; v[i].y -= mean; v[i].z -= mean; v[i].w -= mean;
+      ss = fmaf(v[i].x, v[i].x, ss);
+      ss = fmaf(v[i].y, v[i].y, ss);
+      ss = fmaf(v[i].z, v[i].z, ss);
+      ss = fmaf(v[i].w, v[i].w, ss);
+    }
+  }
+  const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)dim + eps);
+#pragma unroll
+  for (int pass = 0; pass < 2; ++pass) {
+    const float* gw = pass ? w2 : w;
+    TO* o = (pass ? out2 : out);
+    if (o == nullptr) continue;
+    o += (size_t)r * dim;
+#pragma unroll
+    for (int i = 0; i < PER_THREAD; ++i) {
+      const int c = threadIdx.x + i * blockDim.x;
+      if (c >= n4) continue;
+      const float4 g = reinterpret_cast<const float4*>(gw)[c];
+      const float a = (v[i].x * inv) * g.x, b = (v[i].y * inv) * g.y, cc = (v[i].z * inv) * g.z, d = (v[i].w * inv) * g.w;
+      if constexpr (sizeof(TO) == 4) {
+        reinterpret_cast<float4*>(o)[c] = make_float4(a, b, cc, d);
+      } else {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(cc, d);
+        uint2 pk;
+        pk.x = *reinterpret_cast<uint32_t*>(&lo);
+        pk.y = *reinterpret_cast<uint32_t*>(&hi);
+        reinterpret_cast<uint2*>(o)[c] = pk;
+      }
+    }
+  }
+}
+
 // v <- cap * tanh(v / cap), in place, float32.
 __global__ void softcap_kernel(float* __restrict__ v, long long row_stride, int cols, size_t total, float cap) {
   pdl_enter();
@@ -324,20 +383,37 @@ extern "C" int slb_gated_act(const void* gu, void* act, int dtype, int tokens, i
   return check_launch("gated_act");
 }
 
-extern "C" int slb_layernorm(const float* x, const float* w, void* out, int out_dtype, const int* rows, int n_rows,
-                             int dim, float eps, void* stream) {
+// w2 / out2: a second gain and output for the same rows (both null: one norm). out may be x itself when out2 is null.
+extern "C" int slb_layernorm(const float* x, const float* w, void* out, const float* w2, void* out2, int out_dtype,
+                             const int* rows, int n_rows, int dim, float eps, void* stream) {
   SLB_REQUIRE(n_rows >= 0 && dim > 0 && dim <= 12288 && eps > 0.0f, "layernorm: rows=%d dim=%d (at most 12288) eps=%g", n_rows, dim,
               (double)eps);
+  SLB_REQUIRE((w2 == nullptr) == (out2 == nullptr), "layernorm: a second gain and a second output go together");
+  SLB_REQUIRE(out_dtype == kF32 || out_dtype == kBF16, "layernorm: unknown dtype %d", out_dtype);
   if (n_rows == 0) return 0;
   cudaStream_t s = (cudaStream_t)stream;
+  const bool aligned = ((uintptr_t)x | (uintptr_t)w | (uintptr_t)out | (uintptr_t)w2 | (uintptr_t)out2) % 16 == 0;
+  if (dim % 4 == 0 && dim <= 8192 && aligned) {
+    const int n4 = dim / 4;
+    const int threads = n4 <= 64 ? 64 : (n4 <= 128 ? 128 : 256);      // one shape whatever the row count: the same sums in every step
+    const int per = (n4 + threads - 1) / threads;      // at most 8
+    #define SLB_LNORM(P)                                                                                              \
+      if (out_dtype == kF32) launch(layernorm_vec_kernel<float, P>, dim3(n_rows), dim3(threads), 0, s, x, w, (float*)out, w2, (float*)out2, rows, dim, eps); \
+      else launch(layernorm_vec_kernel<__nv_bfloat16, P>, dim3(n_rows), dim3(threads), 0, s, x, w, (__nv_bfloat16*)out, w2, (__nv_bfloat16*)out2, rows, dim, eps)
+    if (per <= 1) { SLB_LNORM(1); } else if (per <= 2) { SLB_LNORM(2); } else if (per <= 4) { SLB_LNORM(4); } else { SLB_LNORM(8); }
+    #undef SLB_LNORM
+    return check_launch("layernorm");
+  }
   const int threads = norm_threads(dim);
   const size_t smem = (size_t)dim * sizeof(float);
-  if (out_dtype == kF32)
-    launch(layernorm_kernel<float>, dim3(n_rows), dim3(threads), smem, s, x, w, (float*)out, rows, dim, eps);
-  else if (out_dtype == kBF16)
-    launch(layernorm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), smem, s, x, w, (__nv_bfloat16*)out, rows, dim, eps);
-  else
-    return fail(1, "layernorm: unknown dtype %d", out_dtype);
+  for (int pass = 0; pass < (out2 ? 2 : 1); ++pass) {
+    const float* gw = pass ? w2 : w;
+    void* o = pass ? out2 : out;
+    if (out_dtype == kF32)
+      launch(layernorm_kernel<float>, dim3(n_rows), dim3(threads), smem, s, x, gw, (float*)o, rows, dim, eps);
+    else
+      launch(layernorm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), smem, s, x, gw, (__nv_bfloat16*)o, rows, dim, eps);
+  }
   return check_launch("layernorm");
 }
 

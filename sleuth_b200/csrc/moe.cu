@@ -665,12 +665,13 @@ extern "C" int slb_moe_experts_tc(const void* h, const void* w_gu, const void* w
 }
 
 // choice, place, list: int32 [tokens * top]; weight: float32 [tokens * top]; counts: int32 [E] (written here).
-// logits: float32 scratch [tokens, E], or null (then every token's block forms its own logits). tiles: int32
+// logits: float32 scratch [tokens, E], or null (then every token's block forms its own logits); with logits_ready they
+// hold the logits already (a matrix product formed them) and nothing is computed from h. tiles: int32
 // [1 + 3 * (tokens * top / 128 + min(tokens * top, E))] for the grouped tensor-memory product, or null.
 extern "C" int slb_moe_route(const void* h, const float* w_router, const float* bias, int* choice, float* weight,
                              int* rank, int* counts, int* place, int* list, float* logits, int* tiles, int layout,
                              int tokens, int dim, int E, int top, int scoring, int groups, int keep, float route_scale,
-                             int dtype, void* stream) {
+                             int logits_ready, int dtype, void* stream) {
   SLB_REQUIRE(tokens >= 0 && dim > 0 && E > 0 && top > 0 && top <= E, "moe_route: tokens=%d dim=%d experts=%d top=%d",
               tokens, dim, E, top);
   SLB_REQUIRE(E <= 4096, "moe_route: at most 4096 experts, got %d", E);
@@ -689,7 +690,10 @@ extern "C" int slb_moe_route(const void* h, const float* w_router, const float* 
   const dim3 grid(tokens), block(256);
   // from a few tokens on the logits are formed 32 tokens and 16 experts at a time, each weight read once a block
   const float* given = nullptr;
-  if (logits != nullptr && tokens < 16) {         // few tokens: a warp per (token, expert)
+  if (logits_ready) {                             // a product in front of this call has formed the logits
+    SLB_REQUIRE(logits != nullptr && bias == nullptr, "moe_route: ready logits must be given, and hold their bias already");
+    given = logits;
+  } else if (logits != nullptr && tokens < 16) {         // few tokens: a warp per (token, expert)
     const dim3 lg((tokens * E + 7) / 8), lb(256);
     if (dtype == kF32) launch(moe_logits_few_kernel<float>, lg, lb, 0, s, (const float*)h, w_router, bias, logits, tokens, dim, E);
     else launch(moe_logits_few_kernel<__nv_bfloat16>, lg, lb, 0, s, (const __nv_bfloat16*)h, w_router, bias, logits, tokens, dim, E);

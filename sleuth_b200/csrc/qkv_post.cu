@@ -223,9 +223,9 @@ static int launch_qkv_post(const QkvPostArgs& a, cudaStream_t s) {
 // (all heads of q together, all heads of k together, before they are split; gains [H * dk] and [G * dk]), then the
 // rotation of the first rot_dim channels of each head, pairing channel i with i + rot_dim/2 (halves) or channel 2i with
 // 2i + 1 (neighbours): (a, b) -> (a cos - b sin, b cos + a sin) with the angle of pair i from the tables
-// [positions, rot_dim / 2]. Values are stored as they are. One block per token; float32 between the load and the one
-// rounding at the store; the sums of squares are formed head by head by one warp each and joined in head order, so a
-// token's result depends on nothing but its own row.
+// [positions, rot_dim / 2]. Values are stored as they are. Float32 between the load and the one rounding at the store;
+// the sums of squares are formed in an order that the row's layout alone fixes, so a token's result depends on nothing
+// but its own row.
 struct QkvSpanArgs {
   const float* qkv;         // [tokens, H * dk + G * dk + G * dv]
   const float* q_gain;      // null: no norm
@@ -247,18 +247,49 @@ struct QkvSpanArgs {
 
 constexpr int kSpanMaxHeads = 512;     // q heads + kv heads
 
-template <typename T>
+// grid (tokens, slices): a slice takes a share of the token's heads, so that a step of few tokens still fills the SMs;
+// every slice forms the sums of squares it needs itself, in the same order, from the same row. QUAD (neighbour pairing,
+// key, value and rotated widths multiples of 4, aligned tensors): a thread takes four channels, two pairs, per step.
+template <typename T, bool QUAD>
 __global__ void __launch_bounds__(256) qkv_post_span_kernel(QkvSpanArgs a) {
   pdl_enter();
   __shared__ float head_ss[kSpanMaxHeads];
-  __shared__ float inv_q, inv_k;
+  __shared__ float scratch[33];
   const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int H = a.heads, G = a.kv_heads, dk = a.key_dim, dv = a.value_dim;
   const size_t row_len = (size_t)(H + G) * dk + (size_t)G * dv;
   const float* row = a.qkv + (size_t)t * row_len;
   const bool normed = a.q_gain != nullptr;
-  if (normed) {
-    for (int hh = warp; hh < H + G; hh += 8) {
+  // the token's place in the cache is looked up first: these dependent loads then overlap the row's
+  const int pos = a.tok_pos[t];
+  const int page = a.k_pool != nullptr ? a.block_table[(size_t)a.tok_seq[t] * a.table_stride + pos / kPageTokens] : 0;
+  const int nthreads = blockDim.x, nwarps = blockDim.x >> 5;
+  const int per_slice = (H + G + gridDim.y - 1) / gridDim.y;
+  const int hh0 = blockIdx.y * per_slice, hh1 = min(H + G, hh0 + per_slice);
+  float inv_q = 1.0f, inv_k = 1.0f;
+  if (normed && a.whole) {
+    const int nq = H * dk, nk = G * dk;
+    float sq = 0.0f, sk = 0.0f;
+    if constexpr (QUAD) {
+      const float4* r4 = reinterpret_cast<const float4*>(row);
+      for (int i = threadIdx.x; i < nq / 4; i += nthreads) {
+        const float4 v = r4[i];
+        sq = fmaf(v.x, v.x, sq); sq = fmaf(v.y, v.y, sq); sq = fmaf(v.z, v.z, sq); sq = fmaf(v.w, v.w, sq);
+      }
+      for (int i = threadIdx.x; i < nk / 4; i += nthreads) {
+        const float4 v = r4[nq / 4 + i];
+        sk = fmaf(v.x, v.x, sk); sk = fmaf(v.y, v.y, sk); sk = fmaf(v.z, v.z, sk); sk = fmaf(v.w, v.w, sk);
+      }
+    } else {
+      for (int i = threadIdx.x; i < nq; i += nthreads) sq = fmaf(row[i], row[i], sq);
+      for (int i = threadIdx.x; i < nk; i += nthreads) sk = fmaf(row[nq + i], row[nq + i], sk);
+    }
+    sq = block_sum(sq, scratch);
+    sk = block_sum(sk, scratch);
+    inv_q = 1.0f / sqrtf(sq / (float)nq + a.eps);
+    inv_k = 1.0f / sqrtf(sk / (float)nk + a.eps);
+  } else if (normed) {
+    for (int hh = hh0 + warp; hh < hh1; hh += nwarps) {
       const float* src = row + (size_t)hh * dk;
       float ss = 0.0f;
       for (int c = lane; c < dk; c += 32) ss = fmaf(src[c], src[c], ss);
@@ -266,63 +297,86 @@ __global__ void __launch_bounds__(256) qkv_post_span_kernel(QkvSpanArgs a) {
       if (lane == 0) head_ss[hh] = ss;
     }
     __syncthreads();
-    if (a.whole && threadIdx.x == 0) {
-      float sq = 0.0f, sk = 0.0f;
-      for (int hh = 0; hh < H; ++hh) sq += head_ss[hh];
-      for (int hh = H; hh < H + G; ++hh) sk += head_ss[hh];
-      inv_q = 1.0f / sqrtf(sq / (float)(H * dk) + a.eps);
-      inv_k = 1.0f / sqrtf(sk / (float)(G * dk) + a.eps);
-    }
-    __syncthreads();
   }
-  const int pos = a.tok_pos[t];
   const int half_rot = a.cos_table ? a.rot_dim >> 1 : 0;
   const float* cs = a.cos_table ? a.cos_table + (size_t)pos * half_rot : nullptr;
   const float* sn = a.cos_table ? a.sin_table + (size_t)pos * half_rot : nullptr;
   T* kdst = nullptr;
   T* vdst = nullptr;
   if (a.k_pool != nullptr) {
-    const int page = a.block_table[(size_t)a.tok_seq[t] * a.table_stride + pos / kPageTokens];
     const size_t slot = (size_t)page * G * kPageTokens + (pos % kPageTokens);      // + head * 64, in rows
     kdst = (T*)a.k_pool + slot * dk;
     vdst = (T*)a.v_pool + slot * dv;
   }
-  const int pairs_per_head = dk >> 1;
-  for (int item = threadIdx.x; item < (H + G) * pairs_per_head; item += blockDim.x) {
-    const int hh = item / pairs_per_head, pi = item - hh * pairs_per_head;
-    const bool is_q = hh < H;
-    if (!is_q && kdst == nullptr) continue;
-    int c0, c1;
-    const bool turns = pi < half_rot;
-    if (turns) {
-      c0 = a.neighbours ? 2 * pi : pi;
-      c1 = a.neighbours ? 2 * pi + 1 : pi + half_rot;
-    } else {
-      c0 = 2 * half_rot + 2 * (pi - half_rot);
-      c1 = c0 + 1;
+  if constexpr (QUAD) {
+    const int quads = dk >> 2;
+    for (int item = threadIdx.x; item < (hh1 - hh0) * quads; item += nthreads) {
+      const int hh = hh0 + item / quads, c = (item % quads) * 4;
+      const bool is_q = hh < H;
+      if (!is_q && kdst == nullptr) continue;
+      float4 v = *reinterpret_cast<const float4*>(row + (size_t)hh * dk + c);
+      if (normed) {
+        const float inv = a.whole ? (is_q ? inv_q : inv_k) : 1.0f / sqrtf(head_ss[hh] / (float)dk + a.eps);
+        const float* gain = (is_q ? a.q_gain : a.k_gain) + (a.whole ? (is_q ? hh : hh - H) * dk : 0);
+        const float4 g = *reinterpret_cast<const float4*>(gain + c);
+        v.x = (v.x * inv) * g.x; v.y = (v.y * inv) * g.y; v.z = (v.z * inv) * g.z; v.w = (v.w * inv) * g.w;
+      }
+      if (c < 2 * half_rot) {
+        const float2 co = *reinterpret_cast<const float2*>(cs + (c >> 1)), si = *reinterpret_cast<const float2*>(sn + (c >> 1));
+        const float x0 = v.x * co.x - v.y * si.x, x1 = v.y * co.x + v.x * si.x;
+        const float x2 = v.z * co.y - v.w * si.y, x3 = v.w * co.y + v.z * si.y;
+        v = make_float4(x0, x1, x2, x3);
+      }
+      T* dst = (is_q ? (T*)a.q_out + ((size_t)t * H + hh) * dk : kdst + (size_t)(hh - H) * kPageTokens * dk) + c;
+      if constexpr (sizeof(T) == 4) {
+        *reinterpret_cast<float4*>(dst) = v;
+      } else {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+        uint2 pk;
+        pk.x = *reinterpret_cast<uint32_t*>(&lo);
+        pk.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(dst) = pk;
+      }
     }
-    const float* src = row + (size_t)hh * dk;
-    float x0 = src[c0], x1 = src[c1];
-    if (normed) {
-      const float inv = a.whole ? (is_q ? inv_q : inv_k) : 1.0f / sqrtf(head_ss[hh] / (float)dk + a.eps);
-      const float* gain = is_q ? a.q_gain : a.k_gain;
-      const int g0 = a.whole ? (is_q ? hh : hh - H) * dk : 0;
-      x0 = (x0 * inv) * gain[g0 + c0];
-      x1 = (x1 * inv) * gain[g0 + c1];
+  } else {
+    const int pairs_per_head = dk >> 1;
+    for (int item = threadIdx.x; item < (hh1 - hh0) * pairs_per_head; item += nthreads) {
+      const int hh = hh0 + item / pairs_per_head, pi = item % pairs_per_head;
+      const bool is_q = hh < H;
+      if (!is_q && kdst == nullptr) continue;
+      int c0, c1;
+      const bool turns = pi < half_rot;
+      if (turns) {
+        c0 = a.neighbours ? 2 * pi : pi;
+        c1 = a.neighbours ? 2 * pi + 1 : pi + half_rot;
+      } else {
+        c0 = 2 * half_rot + 2 * (pi - half_rot);
+        c1 = c0 + 1;
+      }
+      const float* src = row + (size_t)hh * dk;
+      float x0 = src[c0], x1 = src[c1];
+      if (normed) {
+        const float inv = a.whole ? (is_q ? inv_q : inv_k) : 1.0f / sqrtf(head_ss[hh] / (float)dk + a.eps);
+        const float* gain = is_q ? a.q_gain : a.k_gain;
+        const int g0 = a.whole ? (is_q ? hh : hh - H) * dk : 0;
+        x0 = (x0 * inv) * gain[g0 + c0];
+        x1 = (x1 * inv) * gain[g0 + c1];
+      }
+      if (turns) {
+        const float co = cs[pi], si = sn[pi];
+        const float y0 = x0 * co - x1 * si, y1 = x1 * co + x0 * si;
+        x0 = y0;
+        x1 = y1;
+      }
+      T* dst = is_q ? (T*)a.q_out + ((size_t)t * H + hh) * dk : kdst + (size_t)(hh - H) * kPageTokens * dk;
+      dst[c0] = from_f32<T>(x0);
+      dst[c1] = from_f32<T>(x1);
     }
-    if (turns) {
-      const float co = cs[pi], si = sn[pi];
-      const float y0 = x0 * co - x1 * si, y1 = x1 * co + x0 * si;
-      x0 = y0;
-      x1 = y1;
-    }
-    T* dst = is_q ? (T*)a.q_out + ((size_t)t * H + hh) * dk : kdst + (size_t)(hh - H) * kPageTokens * dk;
-    dst[c0] = from_f32<T>(x0);
-    dst[c1] = from_f32<T>(x1);
   }
-  if (vdst != nullptr) {
+  if (vdst != nullptr) {      // the values of the kv heads among this slice's heads (kv head g rides with head H + g)
     const float* src = row + (size_t)(H + G) * dk;
-    for (int i = threadIdx.x; i < G * dv; i += blockDim.x) {
+    const int g0 = max(hh0, H) - H, g1 = hh1 - H;
+    for (int i = g0 * dv + threadIdx.x; i < g1 * dv; i += nthreads) {
       const int g = i / dv, c = i - g * dv;
       vdst[(size_t)g * kPageTokens * dv + c] = from_f32<T>(src[i]);
     }
@@ -383,8 +437,25 @@ extern "C" int slb_qkv_post_span(const float* qkv, const float* q_gain, const fl
   a.tokens = tokens; a.heads = heads; a.kv_heads = kv_heads; a.key_dim = key_dim; a.value_dim = value_dim; a.rot_dim = rot_dim;
   a.neighbours = neighbours ? 1 : 0; a.whole = whole ? 1 : 0; a.eps = eps;
   cudaStream_t s = (cudaStream_t)stream;
-  if (dtype == kF32) launch(qkv_post_span_kernel<float>, dim3(tokens), dim3(256), 0, s, a);
-  else if (dtype == kBF16) launch(qkv_post_span_kernel<__nv_bfloat16>, dim3(tokens), dim3(256), 0, s, a);
-  else return fail(1, "qkv_post_span: unknown dtype %d", dtype);
+  // slices of a token's heads: enough blocks for two per SM when the step brings few tokens (the number depends on the
+  // step's size only; which slice handles a head changes nothing in its result)
+  int slices = (2 * sm_count() + tokens - 1) / tokens;
+  slices = slices < 1 ? 1 : (slices > 16 ? 16 : slices);
+  if (slices > heads + kv_heads) slices = heads + kv_heads;
+  const bool quad = neighbours && key_dim % 4 == 0 && value_dim % 4 == 0 && rot_dim % 4 == 0 &&
+                    ((uintptr_t)qkv | (uintptr_t)q_gain | (uintptr_t)k_gain | (uintptr_t)q_out | (uintptr_t)k_pool) % 16 == 0 &&
+                    ((uintptr_t)cos_table | (uintptr_t)sin_table) % 8 == 0;
+  // many tokens: smaller blocks, so that all of them are resident at once (the float32 run keeps one block shape, so
+  // that a row's sums are formed in the same order in every step)
+  const dim3 grid(tokens, slices), block(dtype == kBF16 && tokens >= 1024 ? 128 : 256);
+  if (dtype == kF32) {
+    if (quad) launch(qkv_post_span_kernel<float, true>, grid, block, 0, s, a);
+    else launch(qkv_post_span_kernel<float, false>, grid, block, 0, s, a);
+  } else if (dtype == kBF16) {
+    if (quad) launch(qkv_post_span_kernel<__nv_bfloat16, true>, grid, block, 0, s, a);
+    else launch(qkv_post_span_kernel<__nv_bfloat16, false>, grid, block, 0, s, a);
+  } else {
+    return fail(1, "qkv_post_span: unknown dtype %d", dtype);
+  }
   return check_launch("qkv_post_span");
 }

@@ -122,6 +122,8 @@ class Engine:
             t = torch.randn(d.shape, generator=gen, device=device, dtype=torch.float32) * std
             if d.init == "gain":
                 t += 1.0
+            if d.role == "vector" and len(d.shape) >= 2 and run_dtype == torch.bfloat16:
+                t = t.to(torch.bfloat16).to(torch.float32)      # a matrix kept in float32 (a router's): values a bfloat16 file holds
             tensors[name] = t.to(run_dtype) if d.role == "matrix" else t
         model.bind(tensors)
         del tensors

@@ -151,7 +151,7 @@ _SIGNATURES = {
     "slb_argmax": [P, L, I, I, P, P, L, P],
     "slb_sample": [P, L, I, I, F, I, F, F, P, P, P],
     "slb_gated_act": [P, P, I, I, I, I, F, F, P],
-    "slb_layernorm": [P, P, P, I, P, I, I, F, P],
+    "slb_layernorm": [P, P, P, P, P, I, P, I, I, F, P],
     "slb_softcap": [P, L, I, I, F, P],
     "slb_qkv_post_span": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P],
     "slb_stream_inject": [P, P, P, I, I, P],
@@ -159,7 +159,7 @@ _SIGNATURES = {
     "slb_head_prompt_attention": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P],
     "slb_latent_attention": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, I, P],
     "slb_latent_gate": [P, P, P, I, I, I, I, P],
-    "slb_moe_route": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, P],
+    "slb_moe_route": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P],
     "slb_moe_experts_tc": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, F, P, P],
     "slb_gemm_skinny_gated": [P, P, P, I, I, I, I, I, F, F, P, L, P, I, P],
     "slb_gemm_tc_gated": [P, P, P, I, I, I, I, I, F, F, P, P],

@@ -101,17 +101,22 @@ def gated_act(gu: torch.Tensor, act: torch.Tensor, kind: str = "silu", stream=No
 
 
 def layernorm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, eps: float, rows: torch.Tensor | None = None,
-              stream=None) -> None:
-    """out[r] = (x[row] - mean) / sqrt(var + eps) * w (a gain, no bias); ``out`` may be ``x`` itself."""
-    _cuda(x, w, out, rows)
+              stream=None, w2: torch.Tensor | None = None, out2: torch.Tensor | None = None) -> None:
+    """out[r] = (x[row] - mean) / sqrt(var + eps) * w (a gain, no bias); ``out`` may be ``x`` itself. With ``w2`` and
+    ``out2``: the same rows once more with another gain, in the same pass (mean and variance are shared)."""
+    _cuda(x, w, out, rows, w2, out2)
     R, d = out.shape
     _need(x.dtype == torch.float32 and w.dtype == torch.float32 and out.dtype in DT, "layernorm: dtypes")
     _need(x.shape[1] == d and w.numel() == d, "layernorm: widths disagree")
+    _need((w2 is None) == (out2 is None), "layernorm: a second gain and a second output go together")
+    if w2 is not None:
+        _need(w2.dtype == torch.float32 and w2.numel() == d and out2.shape == out.shape and out2.dtype == out.dtype
+              and out.data_ptr() != x.data_ptr(), "layernorm: the second gain and output")
     if rows is None:
         _need(x.shape[0] >= R, "layernorm: fewer input rows than output rows")
     else:
         _need(rows.dtype == torch.int32 and rows.numel() >= R, "layernorm: rows must be int32, one per output row")
-    lib().call("slb_layernorm", _p(x), _p(w), _p(out), DT[out.dtype], _p(rows), R, d, float(eps),
+    lib().call("slb_layernorm", _p(x), _p(w), _p(out), _p(w2), _p(out2), DT[out.dtype], _p(rows), R, d, float(eps),
                stream if stream is not None else current_stream())
 
 
@@ -883,7 +888,7 @@ MOE_FEW_PAIRS = 64      # up to this many (token, choice) pairs ``moe_experts`` 
 
 def moe_route(h, w_router, bias, choice, weight, rank, counts, place, order, top: int, stream=None, logits=None,
               tiles=None, layout: bool = True, scoring: str = "softmax_top", groups: int = 1, keep: int = 1,
-              scale: float = 1.0) -> None:
+              scale: float = 1.0, logits_ready: bool = False) -> None:
     """Router logits in float32, then the choice. ``scoring="softmax_top"``: the ``top`` largest logits, weights =
     softmax over those. ``scoring="sigmoid"``: scores = sigmoid(logits); the experts form ``groups`` equal groups of
     neighbours, a group scores the sum of its two largest scores, only experts of the ``keep`` best groups can be
@@ -891,7 +896,8 @@ def moe_route(h, w_router, bias, choice, weight, rank, counts, place, order, top
     pairs are laid out expert by expert: counts [experts], place [T * top] (a pair's row in that order), order
     [T * top] (the pair at each row). choice, rank int32 [T * top]; weight float32 [T * top]. ``logits``: float32
     scratch [T, experts]; with it, steps of many tokens form their logits 32 tokens at a time (the same sums, k
-    ascending). ``layout=False`` leaves counts, place and order unwritten: ``moe_experts`` with ``choice`` does not read
+    ascending). ``logits_ready``: ``logits`` holds the router's logits already (a product formed them; no bias).
+    ``layout=False`` leaves counts, place and order unwritten: ``moe_experts`` with ``choice`` does not read
     them for steps of at most ``MOE_FEW_PAIRS`` pairs."""
     _cuda(h, w_router, bias, choice, weight, rank, counts, place, order, logits, tiles)
     T, d = h.shape
@@ -907,7 +913,7 @@ def moe_route(h, w_router, bias, choice, weight, rank, counts, place, order, top
     _need(tiles is None or (tiles.dtype == torch.int32 and tiles.numel() >= moe_tile_words(T, top, E)), "moe_route: row-tile table")
     lib().call("slb_moe_route", _p(h), _p(w_router), _p(bias), _p(choice), _p(weight), _p(rank), _p(counts), _p(place),
                _p(order), _p(logits), _p(tiles), 1 if layout else 0, T, d, E, int(top), ROUTE_SCORINGS[scoring], int(groups),
-               int(keep), float(scale), DT[h.dtype], stream if stream is not None else current_stream())
+               int(keep), float(scale), 1 if logits_ready else 0, DT[h.dtype], stream if stream is not None else current_stream())
 
 
 def moe_experts(h, w_gate_up, w_down, counts, order, weight, act, y, x, top: int, activation: str = "silu",

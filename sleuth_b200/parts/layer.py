@@ -94,9 +94,16 @@ class ParallelLayer(Part):
     def forward(self, x, b, view, ws):
         mark = ws.mark()
         after = getattr(b, "next_read", None)
-        h = Normed(self.norm1, x, ws, b.stream, self.ctx.dtype).tensor()
-        # the feed-forward's input is formed before the mixer adds into the stream
-        h2 = Normed(self.norm2, x, ws, b.stream, self.ctx.dtype).tensor() if self.norm2 is not None else h
+        # the feed-forward's input is formed before the mixer adds into the stream; two norms that can share a pass do
+        together = getattr(self.norm1, "forward_with", None) if self.norm2 is not None else None
+        h = h2 = None
+        if together is not None:
+            h, h2 = ws.take(x.shape, self.ctx.dtype), ws.take(x.shape, self.ctx.dtype)
+            if not together(self.norm2, x, h, h2, stream=b.stream):
+                h = h2 = None
+        if h is None:
+            h = Normed(self.norm1, x, ws, b.stream, self.ctx.dtype).tensor()
+            h2 = Normed(self.norm2, x, ws, b.stream, self.ctx.dtype).tensor() if self.norm2 is not None else h
         b.next_read = lead_weight_of(self.ffn) if self.ffn is not None else after
         self.mixer.forward(h, x, b, view, ws)
         b.next_read = after

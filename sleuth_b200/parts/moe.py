@@ -21,6 +21,7 @@ import torch
 
 from ..kernels import ops
 from .base import BuildContext, Normed, ParamDecl, Part, build_ffn, register_ffn
+from .linear import Linear
 from .spec import RoutedExpertsSpec
 
 
@@ -46,7 +47,7 @@ class RoutedExperts(Part):
         if spec.activation == "clamped_swish" and not spec.limit > 0:
             raise ValueError(f"routed_experts: the clamped swish needs a positive limit, got {spec.limit}")
         self.spec, self.ctx = spec, ctx
-        self.w_router = self.bias = self.w_gate_up = self.w_down = None
+        self.w_router = self.bias = self.w_gate_up = self.w_down = self.router_product = None
         self.shared = build_ffn(spec.shared, ctx) if spec.shared is not None else None
 
     def lead_weight(self):
@@ -75,6 +76,13 @@ class RoutedExperts(Part):
         self.w_down = torch.stack([t[f"e{e}.down.weight"] for e in range(s.experts)]).to(dt).contiguous()
         if self.shared is not None:
             self.shared.bind({k[len("shared."):]: v for k, v in t.items() if k.startswith("shared.")})
+        # A bfloat16 run whose router matrix is exactly representable in bfloat16 (a file that stores it so) forms the
+        # logits as a product of its own: bfloat16 times bfloat16 is exact in float32 and the sums are float32, so these
+        # are the float32 logits of the same inputs, from the tensor cores instead of a lane per token.
+        self.router_product = None
+        if (dt == torch.bfloat16 and self.bias is None and s.hidden % 32 == 0
+                and torch.equal(self.w_router.to(torch.bfloat16).to(torch.float32), self.w_router)):
+            self.router_product = Linear(self.w_router.to(torch.bfloat16), dt)
 
     def forward(self, h, x, b, ws):
         s, dt = self.spec, self.ctx.dtype
@@ -94,13 +102,15 @@ class RoutedExperts(Part):
         act = ws.take((pairs, s.intermediate), dt)
         y = ws.take((pairs, s.hidden), torch.float32)
         logits = ws.take((T, s.experts), torch.float32)
+        if self.router_product is not None:
+            self.router_product.forward(h, out=logits, ws=ws, stream=b.stream)
         # steps of many pairs: the tcgen05 grouped products (bfloat16, inner sizes that TMA takes)
         grouped = (dt == torch.bfloat16 and pairs >= TC_PAIRS and s.hidden % 8 == 0
                    and s.intermediate % 8 == 0)
         tiles = ws.take((ops.moe_tile_words(T, s.top, s.experts),), torch.int32) if grouped else None
         ops.moe_route(h, self.w_router, self.bias, choice, weight, rank, counts, place, order, s.top, b.stream, logits, tiles,
                       layout=pairs > ops.MOE_FEW_PAIRS, scoring=s.scoring, groups=s.groups, keep=s.keep_groups,
-                      scale=s.route_scale)
+                      scale=s.route_scale, logits_ready=self.router_product is not None)
         if grouped:
             xs = ws.take((pairs, s.hidden), dt)
             ops.moe_experts_tc(h, self.w_gate_up, self.w_down, order, place, weight, tiles, xs, act, y, x, s.top, b.stream,

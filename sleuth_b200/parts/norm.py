@@ -52,6 +52,14 @@ class LayerNorm(Part):
         ops.layernorm(x, self.weight, out, self.eps, rows, stream)
         return out
 
+    def forward_with(self, other, x: torch.Tensor, out: torch.Tensor, out_other: torch.Tensor, stream=None) -> bool:
+        """This norm and ``other`` of the same rows in one pass, when they differ in their gains only (mean and variance
+        are then the same); False when they do not, and nothing has run."""
+        if not (isinstance(other, LayerNorm) and other.eps == self.eps and other.dim == self.dim):
+            return False
+        ops.layernorm(x, self.weight, out, self.eps, None, stream, w2=other.weight, out2=out_other)
+        return True
+
 
 register_norm("rmsnorm", RMSNorm)
 register_norm("layernorm", LayerNorm)

@@ -228,16 +228,21 @@ def test_greedy_generation_through_the_entry_point(name, dtype, rabadra_folders)
     prompts = requests_for(name, [3, 70, 20, 1, 9, 130], seed=6, ref=ref)
     out = eng.generate(prompts, max_new_tokens=12, sampling=sb.SamplingConfig(temperature=0), stop_ids=())
     margin = {"fp32": 1e-3, "bf16": 0.3}[dtype]
-    clear = 0
+    clear = checked = 0
     for ids, r in zip(prompts, out):
         assert len(r.new_ids) == 12
         seq = list(ids)
         for tok in r.new_ids:
+            if dtype == "bf16" and ref.clearness(seq) < CLEAR:
+                break       # a generated token chose its experts by a hair: from here on the two runs may part ways
             top2 = torch.topk(ref(seq)[-1], 2)
+            checked += 1
             if float(top2.values[0] - top2.values[1]) >= margin:
                 assert tok == int(top2.indices[0])
                 clear += 1
             else:
                 assert tok in top2.indices.tolist()
             seq.append(tok)
-    assert clear >= {"fp32": 60, "bf16": 12}[dtype]
+    # enough tokens were held to the plain code's: all of them in float32 (most by a clear margin), in bfloat16 those up
+    # to a request's first close call among the experts
+    assert checked >= {"fp32": 72, "bf16": 30}[dtype] and (dtype == "bf16" or clear >= 60)

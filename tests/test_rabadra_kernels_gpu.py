@@ -31,7 +31,7 @@ def rot_tables(positions, base, dims):
 
 
 @pytest.mark.parametrize("dtype", ["fp32", "bf16"])
-@pytest.mark.parametrize("dim", [72, 320, 1000, 4096])
+@pytest.mark.parametrize("dim", [72, 321, 1000, 4096])
 def test_layer_norm(dim, dtype):
     g = torch.Generator().manual_seed(dim)
     x = (3.0 + 2.0 * torch.randn(11, dim, generator=g)).to(DEV)        # a mean far from zero: subtracting it matters
@@ -44,6 +44,11 @@ def test_layer_norm(dim, dtype):
     some = torch.empty(3, dim, dtype=DT[dtype], device=DEV)
     ops().layernorm(x, w, some, 1e-5, rows)
     torch.testing.assert_close(some.cpu().double(), want[[9, 0, 4]], **TOL[dtype])
+    w2 = (1 + 0.2 * torch.randn(dim, generator=g)).to(DEV)      # two gains in one pass, as a parallel layer's two norms run
+    one, two = torch.empty(11, dim, dtype=DT[dtype], device=DEV), torch.empty(11, dim, dtype=DT[dtype], device=DEV)
+    ops().layernorm(x, w, one, 1e-5, w2=w2, out2=two)
+    torch.testing.assert_close(one.cpu().double(), want, **TOL[dtype])
+    torch.testing.assert_close(two.cpu().double(), plain.layer_norm(x.cpu().double(), w2.cpu().double(), 1e-5), **TOL[dtype])
     if dtype == "fp32":
         ops().layernorm(x, w, x, 1e-5)      # in place, as the embedding's norm runs
         torch.testing.assert_close(x.cpu().double(), want, **TOL[dtype])

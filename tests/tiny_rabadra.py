@@ -56,11 +56,13 @@ SEEDS = {"A": 111, "B": 222, "C": 333, "D": 444}
 STD = 0.08      # wide enough that attention is far from uniform and the experts' shares differ
 
 
-def sharpen(folder, logit_std: float = 2.5, sink_std: float = 1.5) -> None:
+def sharpen(folder, logit_std: float = 2.5, sink_std: float = 1.5, round_router: bool = False) -> None:
     """Rewrite a written folder so that faults show: the routers' rows are scaled until their logits have about
     ``logit_std`` (the scores then spread over (0, 1), the choice changes from token to token, and two scores seldom lie
     closer than a bfloat16 run's rounding of the layer input), and the sinks until they have about ``sink_std`` (a
-    sink that is left out, scaled, or given to the wrong head then moves the result)."""
+    sink that is left out, scaled, or given to the wrong head then moves the result). ``round_router``: the routers'
+    matrices are then rounded to bfloat16 values (kept in float32), as a file that stores bfloat16 weights has them: a
+    bfloat16 run then forms their logits as a product of its own."""
     from pathlib import Path
 
     from plain.qwen3_plain import read_safetensors
@@ -70,6 +72,9 @@ def sharpen(folder, logit_std: float = 2.5, sink_std: float = 1.5) -> None:
     for name, t in tensors.items():
         if name.endswith(".mlp.router"):
             tensors[name] = t * (logit_std / (float(t.float().std()) * t.shape[1] ** 0.5))
+            if round_router:
+                import torch
+                tensors[name] = tensors[name].to(torch.bfloat16).to(t.dtype)
         elif name.endswith(".mix.sink"):
             tensors[name] = t * (sink_std / max(float(t.float().std()), 1e-6))
     write_safetensors(tensors, path, metadata={"format": "pt"})
