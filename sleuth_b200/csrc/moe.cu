@@ -687,7 +687,7 @@ extern "C" int slb_moe_route(const void* h, const float* w_router, const float* 
   (void)rank;      // kept in the signature: callers hand over a table that older versions filled
   const RouteRule rule{scoring, groups, keep, route_scale};
   const size_t smem = (size_t)(E + 2 * groups) * sizeof(float);
-  const dim3 grid(tokens), block(256);
+  const dim3 grid(tokens);
   // from a few tokens on the logits are formed 32 tokens and 16 experts at a time, each weight read once a block
   const float* given = nullptr;
   if (logits_ready) {                             // a product in front of this call has formed the logits
@@ -708,6 +708,8 @@ extern "C" int slb_moe_route(const void* h, const float* w_router, const float* 
     if (rc0) return rc0;
     given = logits;
   }
+  // with the logits given only the choosing warp has work: a block of one warp, so that many tokens are resident at once
+  const dim3 block(given != nullptr && tokens >= 256 ? 32 : 256);
   if (dtype == kF32)
     launch(moe_route_kernel<float>, grid, block, smem, s, (const float*)h, w_router, bias, given, choice, weight, tokens, dim, E, top, rule);
   else
