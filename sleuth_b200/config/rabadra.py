@@ -96,9 +96,10 @@ MIXERS = ("attention",)
 
 
 def _strict(cls, d, where):
-    """``read_fields`` that also refuses keys the class does not name: a key that nobody reads is a part of the model
-    that would silently be left out."""
+    """``read_fields`` that also refuses keys the class does not name (unless their value is null): a key that nobody
+    reads is a part of the model that would silently be left out."""
     obj, unread = read_fields(cls, d, where)
+    unread = [k for k in unread if d[k] is not None]       # a key set to null says that the thing is absent
     if unread:
         raise ConfigError(f"{where}: unknown key(s) {unread}")
     return obj
@@ -128,6 +129,9 @@ class RabadraConfig:
         parsed = []
         for i, raw in enumerate(self.layers):
             where = f"config.json: layers[{i}]"
+            j = raw.get("weights_of") if isinstance(raw, dict) else None
+            if isinstance(j, int) and not isinstance(j, bool) and 0 <= j < len(self.layers) and isinstance(self.layers[j], dict):
+                raw = {**{k: v for k, v in self.layers[j].items() if k != "weights_of"}, **raw}    # what it leaves out is the lender's
             L = _strict(_Layer, raw, where)
             need(L.type in MIXERS, f"layers[{i}].type {L.type!r} is not a known mixer {list(MIXERS)}")
             m = _strict(_Mixer, L.mixer, where + ".mixer")

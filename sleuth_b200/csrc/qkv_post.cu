@@ -248,9 +248,8 @@ struct QkvSpanArgs {
 constexpr int kSpanMaxHeads = 512;     // q heads + kv heads
 
 // grid (tokens, slices): a slice takes a share of the token's heads, so that a step of few tokens still fills the SMs;
-// every slice forms the sums of squares it needs itself, in the same order, from the same row. QUAD (neighbour pairing,
-// key, value and rotated widths multiples of 4, aligned tensors): a thread takes four channels, two pairs, per step.
-template <typename T, bool QUAD>
+// every slice forms the sums of squares it needs itself, in the same order, from the same row.
+template <typename T>
 __global__ void __launch_bounds__(256) qkv_post_span_kernel(QkvSpanArgs a) {
   pdl_enter();
   __shared__ float head_ss[kSpanMaxHeads];
@@ -270,20 +269,8 @@ __global__ void __launch_bounds__(256) qkv_post_span_kernel(QkvSpanArgs a) {
   if (normed && a.whole) {
     const int nq = H * dk, nk = G * dk;
     float sq = 0.0f, sk = 0.0f;
-    if constexpr (QUAD) {
-      const float4* r4 = reinterpret_cast<const float4*>(row);
-      for (int i = threadIdx.x; i < nq / 4; i += nthreads) {
-        const float4 v = r4[i];
-        sq = fmaf(v.x, v.x, sq); sq = fmaf(v.y, v.y, sq); sq = fmaf(v.z, v.z, sq); sq = fmaf(v.w, v.w, sq);
-      }
-      for (int i = threadIdx.x; i < nk / 4; i += nthreads) {
-        const float4 v = r4[nq / 4 + i];
-        sk = fmaf(v.x, v.x, sk); sk = fmaf(v.y, v.y, sk); sk = fmaf(v.z, v.z, sk); sk = fmaf(v.w, v.w, sk);
-      }
-    } else {
-      for (int i = threadIdx.x; i < nq; i += nthreads) sq = fmaf(row[i], row[i], sq);
-      for (int i = threadIdx.x; i < nk; i += nthreads) sk = fmaf(row[nq + i], row[nq + i], sk);
-    }
+    for (int i = threadIdx.x; i < nq; i += nthreads) sq = fmaf(row[i], row[i], sq);
+    for (int i = threadIdx.x; i < nk; i += nthreads) sk = fmaf(row[nq + i], row[nq + i], sk);
     sq = block_sum(sq, scratch);
     sk = block_sum(sk, scratch);
     inv_q = 1.0f / sqrtf(sq / (float)nq + a.eps);
@@ -308,70 +295,38 @@ __global__ void __launch_bounds__(256) qkv_post_span_kernel(QkvSpanArgs a) {
     kdst = (T*)a.k_pool + slot * dk;
     vdst = (T*)a.v_pool + slot * dv;
   }
-  if constexpr (QUAD) {
-    const int quads = dk >> 2;
-    for (int item = threadIdx.x; item < (hh1 - hh0) * quads; item += nthreads) {
-      const int hh = hh0 + item / quads, c = (item % quads) * 4;
-      const bool is_q = hh < H;
-      if (!is_q && kdst == nullptr) continue;
-      float4 v = *reinterpret_cast<const float4*>(row + (size_t)hh * dk + c);
-      if (normed) {
-        const float inv = a.whole ? (is_q ? inv_q : inv_k) : 1.0f / sqrtf(head_ss[hh] / (float)dk + a.eps);
-        const float* gain = (is_q ? a.q_gain : a.k_gain) + (a.whole ? (is_q ? hh : hh - H) * dk : 0);
-        const float4 g = *reinterpret_cast<const float4*>(gain + c);
-        v.x = (v.x * inv) * g.x; v.y = (v.y * inv) * g.y; v.z = (v.z * inv) * g.z; v.w = (v.w * inv) * g.w;
-      }
-      if (c < 2 * half_rot) {
-        const float2 co = *reinterpret_cast<const float2*>(cs + (c >> 1)), si = *reinterpret_cast<const float2*>(sn + (c >> 1));
-        const float x0 = v.x * co.x - v.y * si.x, x1 = v.y * co.x + v.x * si.x;
-        const float x2 = v.z * co.y - v.w * si.y, x3 = v.w * co.y + v.z * si.y;
-        v = make_float4(x0, x1, x2, x3);
-      }
-      T* dst = (is_q ? (T*)a.q_out + ((size_t)t * H + hh) * dk : kdst + (size_t)(hh - H) * kPageTokens * dk) + c;
-      if constexpr (sizeof(T) == 4) {
-        *reinterpret_cast<float4*>(dst) = v;
-      } else {
-        __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
-        uint2 pk;
-        pk.x = *reinterpret_cast<uint32_t*>(&lo);
-        pk.y = *reinterpret_cast<uint32_t*>(&hi);
-        *reinterpret_cast<uint2*>(dst) = pk;
-      }
+  const int pairs_per_head = dk >> 1;
+  for (int item = threadIdx.x; item < (hh1 - hh0) * pairs_per_head; item += nthreads) {
+    const int hh = hh0 + item / pairs_per_head, pi = item % pairs_per_head;
+    const bool is_q = hh < H;
+    if (!is_q && kdst == nullptr) continue;
+    int c0, c1;
+    const bool turns = pi < half_rot;
+    if (turns) {
+      c0 = a.neighbours ? 2 * pi : pi;
+      c1 = a.neighbours ? 2 * pi + 1 : pi + half_rot;
+    } else {
+      c0 = 2 * half_rot + 2 * (pi - half_rot);
+      c1 = c0 + 1;
     }
-  } else {
-    const int pairs_per_head = dk >> 1;
-    for (int item = threadIdx.x; item < (hh1 - hh0) * pairs_per_head; item += nthreads) {
-      const int hh = hh0 + item / pairs_per_head, pi = item % pairs_per_head;
-      const bool is_q = hh < H;
-      if (!is_q && kdst == nullptr) continue;
-      int c0, c1;
-      const bool turns = pi < half_rot;
-      if (turns) {
-        c0 = a.neighbours ? 2 * pi : pi;
-        c1 = a.neighbours ? 2 * pi + 1 : pi + half_rot;
-      } else {
-        c0 = 2 * half_rot + 2 * (pi - half_rot);
-        c1 = c0 + 1;
-      }
-      const float* src = row + (size_t)hh * dk;
-      float x0 = src[c0], x1 = src[c1];
-      if (normed) {
-        const float inv = a.whole ? (is_q ? inv_q : inv_k) : 1.0f / sqrtf(head_ss[hh] / (float)dk + a.eps);
-        const float* gain = is_q ? a.q_gain : a.k_gain;
-        const int g0 = a.whole ? (is_q ? hh : hh - H) * dk : 0;
-        x0 = (x0 * inv) * gain[g0 + c0];
-        x1 = (x1 * inv) * gain[g0 + c1];
-      }
-      if (turns) {
-        const float co = cs[pi], si = sn[pi];
-        const float y0 = x0 * co - x1 * si, y1 = x1 * co + x0 * si;
-        x0 = y0;
-        x1 = y1;
-      }
-      T* dst = is_q ? (T*)a.q_out + ((size_t)t * H + hh) * dk : kdst + (size_t)(hh - H) * kPageTokens * dk;
-      dst[c0] = from_f32<T>(x0);
-      dst[c1] = from_f32<T>(x1);
+    const float* src = row + (size_t)hh * dk;
+    float x0 = src[c0], x1 = src[c1];
+    if (normed) {
+      const float inv = a.whole ? (is_q ? inv_q : inv_k) : 1.0f / sqrtf(head_ss[hh] / (float)dk + a.eps);
+      const float* gain = is_q ? a.q_gain : a.k_gain;
+      const int g0 = a.whole ? (is_q ? hh : hh - H) * dk : 0;
+      x0 = (x0 * inv) * gain[g0 + c0];
+      x1 = (x1 * inv) * gain[g0 + c1];
     }
+    if (turns) {
+      const float co = cs[pi], si = sn[pi];
+      const float y0 = x0 * co - x1 * si, y1 = x1 * co + x0 * si;
+      x0 = y0;
+      x1 = y1;
+    }
+    T* dst = is_q ? (T*)a.q_out + ((size_t)t * H + hh) * dk : kdst + (size_t)(hh - H) * kPageTokens * dk;
+    dst[c0] = from_f32<T>(x0);
+    dst[c1] = from_f32<T>(x1);
   }
   if (vdst != nullptr) {      // the values of the kv heads among this slice's heads (kv head g rides with head H + g)
     const float* src = row + (size_t)(H + G) * dk;
@@ -380,6 +335,135 @@ __global__ void __launch_bounds__(256) qkv_post_span_kernel(QkvSpanArgs a) {
       const int g = i / dv, c = i - g * dv;
       vdst[(size_t)g * kPageTokens * dv + c] = from_f32<T>(src[i]);
     }
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ void store4(T* dst, const float4& v) {
+  if constexpr (sizeof(T) == 4) {
+    *reinterpret_cast<float4*>(dst) = v;
+  } else {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 pk;
+    pk.x = *reinterpret_cast<uint32_t*>(&lo);
+    pk.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(dst) = pk;
+  }
+}
+
+// The form for neighbour pairing with key, value and rotated widths that are multiples of 4 and 16-byte aligned
+// tensors: a thread takes four channels (two pairs) per item and keeps its at most MAXI items of the slice, with their
+// gains and angles, in registers from the first pass on; every load is asked for before the sums of squares are
+// joined, so a block waits for memory about twice instead of once per pass and table. When one slice holds the whole
+// row (steps of many tokens) the sums come from those registers too and the row is read once.
+template <typename T, int MAXI>
+__global__ void __launch_bounds__(256) qkv_post_span_quad_kernel(QkvSpanArgs a) {
+  pdl_enter();
+  __shared__ float head_ss[kSpanMaxHeads];
+  __shared__ float scratch[33];
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int H = a.heads, G = a.kv_heads, dk = a.key_dim, dv = a.value_dim;
+  const size_t row_len = (size_t)(H + G) * dk + (size_t)G * dv;
+  const float* row = a.qkv + (size_t)t * row_len;
+  const float4* row4 = reinterpret_cast<const float4*>(row);
+  const bool normed = a.q_gain != nullptr;
+  const int pos = a.tok_pos[t];
+  const int page = a.k_pool != nullptr ? a.block_table[(size_t)a.tok_seq[t] * a.table_stride + pos / kPageTokens] : 0;
+  const int nthreads = blockDim.x, nwarps = blockDim.x >> 5;
+  const int per_slice = (H + G + gridDim.y - 1) / gridDim.y;
+  const int hh0 = blockIdx.y * per_slice, hh1 = min(H + G, hh0 + per_slice);
+  const int quads = dk >> 2, n_items = (hh1 - hh0) * quads;
+  const int half_rot = a.cos_table ? a.rot_dim >> 1 : 0;
+  const float* cs = a.cos_table ? a.cos_table + (size_t)pos * half_rot : nullptr;
+  const float* sn = a.cos_table ? a.sin_table + (size_t)pos * half_rot : nullptr;
+
+  float4 v[MAXI], g[MAXI];
+  float2 co[MAXI], si[MAXI];
+#pragma unroll
+  for (int i = 0; i < MAXI; ++i) {
+    const int item = threadIdx.x + i * nthreads;
+    v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    g[i] = make_float4(1.f, 1.f, 1.f, 1.f);
+    co[i] = make_float2(1.f, 1.f);
+    si[i] = make_float2(0.f, 0.f);
+    if (item < n_items) {
+      const int hh = hh0 + item / quads, c = (item % quads) * 4;
+      v[i] = row4[hh0 * quads + item];
+      if (normed) {
+        const bool is_q = hh < H;
+        const float* gain = (is_q ? a.q_gain : a.k_gain) + (a.whole ? (is_q ? hh : hh - H) * dk : 0);
+        g[i] = *reinterpret_cast<const float4*>(gain + c);
+      }
+      if (c < 2 * half_rot) {
+        co[i] = *reinterpret_cast<const float2*>(cs + (c >> 1));
+        si[i] = *reinterpret_cast<const float2*>(sn + (c >> 1));
+      }
+    }
+  }
+  T* kdst = nullptr;
+  if (a.k_pool != nullptr) {
+    const size_t slot = (size_t)page * G * kPageTokens + (pos % kPageTokens);      // + head * 64, in rows
+    kdst = (T*)a.k_pool + slot * dk;
+    // the values of the kv heads among this slice's heads (kv head g rides with head H + g): nothing to wait for
+    T* vdst = (T*)a.v_pool + slot * dv;
+    const float4* src4 = reinterpret_cast<const float4*>(row + (size_t)(H + G) * dk);
+    const int vq = dv >> 2, g0 = max(hh0, H) - H, g1 = hh1 - H;
+    for (int i = g0 * vq + threadIdx.x; i < g1 * vq; i += nthreads) {
+      const int gh = i / vq, c = (i - gh * vq) * 4;
+      store4<T>(vdst + (size_t)gh * kPageTokens * dv + c, src4[i]);
+    }
+  }
+  float inv_q = 1.0f, inv_k = 1.0f;
+  if (normed && a.whole) {
+    const int nq4 = H * quads, nk4 = G * quads;
+    float sq = 0.0f, sk = 0.0f;
+    if (gridDim.y == 1) {         // this block holds the whole row: item i is float4 i of the row
+#pragma unroll
+      for (int i = 0; i < MAXI; ++i) {
+        const int item = threadIdx.x + i * nthreads;
+        const float ss = fmaf(v[i].x, v[i].x, fmaf(v[i].y, v[i].y, fmaf(v[i].z, v[i].z, v[i].w * v[i].w)));
+        if (item < nq4) sq += ss; else sk += ss;      // items past the row hold zeros
+      }
+    } else {
+      for (int i = threadIdx.x; i < nq4 + nk4; i += nthreads) {      // the same values to the same threads as above
+        const float4 x = row4[i];
+        const float ss = fmaf(x.x, x.x, fmaf(x.y, x.y, fmaf(x.z, x.z, x.w * x.w)));
+        if (i < nq4) sq += ss; else sk += ss;
+      }
+    }
+    sq = block_sum(sq, scratch);
+    sk = block_sum(sk, scratch);
+    inv_q = 1.0f / sqrtf(sq / (float)(H * dk) + a.eps);
+    inv_k = 1.0f / sqrtf(sk / (float)(G * dk) + a.eps);
+  } else if (normed) {
+    for (int hh = hh0 + warp; hh < hh1; hh += nwarps) {
+      const float* src = row + (size_t)hh * dk;
+      float ss = 0.0f;
+      for (int c = lane; c < dk; c += 32) ss = fmaf(src[c], src[c], ss);
+      ss = warp_sum(ss);
+      if (lane == 0) head_ss[hh] = ss;
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < MAXI; ++i) {
+    const int item = threadIdx.x + i * nthreads;
+    if (item >= n_items) continue;
+    const int hh = hh0 + item / quads, c = (item % quads) * 4;
+    const bool is_q = hh < H;
+    if (!is_q && kdst == nullptr) continue;
+    float4 x = v[i];
+    if (normed) {
+      const float inv = a.whole ? (is_q ? inv_q : inv_k) : 1.0f / sqrtf(head_ss[hh] / (float)dk + a.eps);
+      x.x = (x.x * inv) * g[i].x; x.y = (x.y * inv) * g[i].y; x.z = (x.z * inv) * g[i].z; x.w = (x.w * inv) * g[i].w;
+    }
+    if (c < 2 * half_rot) {
+      const float x0 = x.x * co[i].x - x.y * si[i].x, x1 = x.y * co[i].x + x.x * si[i].x;
+      const float x2 = x.z * co[i].y - x.w * si[i].y, x3 = x.w * co[i].y + x.z * si[i].y;
+      x = make_float4(x0, x1, x2, x3);
+    }
+    T* dst = (is_q ? (T*)a.q_out + ((size_t)t * H + hh) * dk : kdst + (size_t)(hh - H) * kPageTokens * dk) + c;
+    store4<T>(dst, x);
   }
 }
 
@@ -442,18 +526,26 @@ extern "C" int slb_qkv_post_span(const float* qkv, const float* q_gain, const fl
   int slices = (2 * sm_count() + tokens - 1) / tokens;
   slices = slices < 1 ? 1 : (slices > 16 ? 16 : slices);
   if (slices > heads + kv_heads) slices = heads + kv_heads;
-  const bool quad = neighbours && key_dim % 4 == 0 && value_dim % 4 == 0 && rot_dim % 4 == 0 &&
-                    ((uintptr_t)qkv | (uintptr_t)q_gain | (uintptr_t)k_gain | (uintptr_t)q_out | (uintptr_t)k_pool) % 16 == 0 &&
-                    ((uintptr_t)cos_table | (uintptr_t)sin_table) % 8 == 0;
+  const bool aligned = ((uintptr_t)qkv | (uintptr_t)q_gain | (uintptr_t)k_gain | (uintptr_t)q_out | (uintptr_t)k_pool |
+                        (uintptr_t)v_pool) % 16 == 0 && ((uintptr_t)cos_table | (uintptr_t)sin_table) % 8 == 0;
   // many tokens: smaller blocks, so that all of them are resident at once (the float32 run keeps one block shape, so
   // that a row's sums are formed in the same order in every step)
-  const dim3 grid(tokens, slices), block(dtype == kBF16 && tokens >= 1024 ? 128 : 256);
-  if (dtype == kF32) {
-    if (quad) launch(qkv_post_span_kernel<float, true>, grid, block, 0, s, a);
-    else launch(qkv_post_span_kernel<float, false>, grid, block, 0, s, a);
+  const int threads = dtype == kBF16 && tokens >= 1024 ? 128 : 256;
+  const int per_slice = (heads + kv_heads + slices - 1) / slices;
+  const int items = (per_slice * (key_dim / 4) + threads - 1) / threads;      // four-channel items a thread holds
+  const bool quad = neighbours && key_dim % 4 == 0 && value_dim % 4 == 0 && rot_dim % 4 == 0 && aligned && items <= 8 &&
+                    (dtype == kF32 || dtype == kBF16);
+  const dim3 grid(tokens, slices), block(threads);
+  if (quad && dtype == kF32) {
+    if (items <= 4) launch(qkv_post_span_quad_kernel<float, 4>, grid, block, 0, s, a);
+    else launch(qkv_post_span_quad_kernel<float, 8>, grid, block, 0, s, a);
+  } else if (quad) {
+    if (items <= 4) launch(qkv_post_span_quad_kernel<__nv_bfloat16, 4>, grid, block, 0, s, a);
+    else launch(qkv_post_span_quad_kernel<__nv_bfloat16, 8>, grid, block, 0, s, a);
+  } else if (dtype == kF32) {
+    launch(qkv_post_span_kernel<float>, grid, block, 0, s, a);
   } else if (dtype == kBF16) {
-    if (quad) launch(qkv_post_span_kernel<__nv_bfloat16, true>, grid, block, 0, s, a);
-    else launch(qkv_post_span_kernel<__nv_bfloat16, false>, grid, block, 0, s, a);
+    launch(qkv_post_span_kernel<__nv_bfloat16>, grid, block, 0, s, a);
   } else {
     return fail(1, "qkv_post_span: unknown dtype %d", dtype);
   }

@@ -80,7 +80,7 @@ class RoutedExperts(Part):
         # logits as a product of its own: bfloat16 times bfloat16 is exact in float32 and the sums are float32, so these
         # are the float32 logits of the same inputs, from the tensor cores instead of a lane per token.
         self.router_product = None
-        if (dt == torch.bfloat16 and self.bias is None and s.hidden % 32 == 0
+        if (dt == torch.bfloat16 and self.bias is None and s.hidden % 32 == 0 and s.experts >= 8
                 and torch.equal(self.w_router.to(torch.bfloat16).to(torch.float32), self.w_router)):
             self.router_product = Linear(self.w_router.to(torch.bfloat16), dt)
 
@@ -102,15 +102,20 @@ class RoutedExperts(Part):
         act = ws.take((pairs, s.intermediate), dt)
         y = ws.take((pairs, s.hidden), torch.float32)
         logits = ws.take((T, s.experts), torch.float32)
-        if self.router_product is not None:
+        # few tokens and few experts: the choosing kernel forms its token's logits itself (a warp per expert, eight at a
+        # time), one launch instead of two; more experts than that, and a block per token would walk them too long
+        own_logits = T < 16 and s.experts <= 32
+        ready = self.router_product is not None and not own_logits
+        if ready:
             self.router_product.forward(h, out=logits, ws=ws, stream=b.stream)
         # steps of many pairs: the tcgen05 grouped products (bfloat16, inner sizes that TMA takes)
         grouped = (dt == torch.bfloat16 and pairs >= TC_PAIRS and s.hidden % 8 == 0
                    and s.intermediate % 8 == 0)
         tiles = ws.take((ops.moe_tile_words(T, s.top, s.experts),), torch.int32) if grouped else None
-        ops.moe_route(h, self.w_router, self.bias, choice, weight, rank, counts, place, order, s.top, b.stream, logits, tiles,
+        ops.moe_route(h, self.w_router, self.bias, choice, weight, rank, counts, place, order, s.top, b.stream,
+                      None if own_logits else logits, tiles,
                       layout=pairs > ops.MOE_FEW_PAIRS, scoring=s.scoring, groups=s.groups, keep=s.keep_groups,
-                      scale=s.route_scale, logits_ready=self.router_product is not None)
+                      scale=s.route_scale, logits_ready=ready)
         if grouped:
             xs = ws.take((pairs, s.hidden), dt)
             ops.moe_experts_tc(h, self.w_gate_up, self.w_down, order, place, weight, tiles, xs, act, y, x, s.top, b.stream,

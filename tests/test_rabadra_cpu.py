@@ -43,6 +43,9 @@ def test_borrowed_weights_become_a_schedule_with_caches_of_their_own():
     assert len(a.layers) == 2 and [(e.layer, e.cache) for e in a.schedule] == [(0, 0), (1, 1), (0, 2)]
     b = spec_of(tr.B)
     assert len(b.layers) == 2 and [(e.layer, e.cache) for e in b.schedule] == [(0, 0), (1, 1), (1, 2), (0, 3)]
+    short = copy.deepcopy(tr.A)
+    short["layers"][2] = {"weights_of": 0}                               # what a borrower leaves out is the lender's
+    assert [(e.layer, e.cache) for e in spec_of(short).schedule] == [(0, 0), (1, 1), (0, 2)]
     chain = copy.deepcopy(tr.A)
     chain["layers"].append(dict(chain["layers"][2], weights_of=2))       # borrows from a borrower
     assert [(e.layer, e.cache) for e in spec_of(chain).schedule] == [(0, 0), (1, 1), (0, 2), (0, 3)]
@@ -77,6 +80,17 @@ def test_what_the_configuration_refuses(edit, words):
     cfg = copy.deepcopy(tr.A)
     edit(cfg)
     with pytest.raises(ConfigError, match=words):
+        spec_of(cfg)
+
+
+def test_a_key_set_to_null_is_absent_and_an_unknown_one_with_a_value_is_refused():
+    cfg = copy.deepcopy(tr.A)
+    cfg["layers"][0]["mixer"]["window"] = None
+    cfg["layers"][0]["mlp"]["router"]["bias"] = None
+    cfg["layers"][1]["weights_of"] = None
+    assert len(spec_of(cfg).layers) == 2
+    cfg["layers"][0]["mlp"]["router"]["bias"] = True
+    with pytest.raises(ConfigError, match="unknown key"):
         spec_of(cfg)
 
 
