@@ -240,6 +240,8 @@ struct QkvSpanArgs {
   const int* block_table;
   int table_stride;
   int tokens, heads, kv_heads, key_dim, value_dim, rot_dim;
+  int norm_dim;             // channels of a head that count in the norms' means (key_dim, or fewer when the heads
+                            // carry zero channels at their end that only pad them to a width the kernels take)
   int neighbours;           // 1: pairs (2i, 2i + 1); 0: pairs (i, i + rot / 2)
   int whole;                // 1: one norm over the whole projection; 0: one per head
   float eps;
@@ -273,8 +275,8 @@ __global__ void __launch_bounds__(256) qkv_post_span_kernel(QkvSpanArgs a) {
     for (int i = threadIdx.x; i < nk; i += nthreads) sk = fmaf(row[nq + i], row[nq + i], sk);
     sq = block_sum(sq, scratch);
     sk = block_sum(sk, scratch);
-    inv_q = 1.0f / sqrtf(sq / (float)nq + a.eps);
-    inv_k = 1.0f / sqrtf(sk / (float)nk + a.eps);
+    inv_q = 1.0f / sqrtf(sq / (float)(H * a.norm_dim) + a.eps);
+    inv_k = 1.0f / sqrtf(sk / (float)(G * a.norm_dim) + a.eps);
   } else if (normed) {
     for (int hh = hh0 + warp; hh < hh1; hh += nwarps) {
       const float* src = row + (size_t)hh * dk;
@@ -312,7 +314,7 @@ __global__ void __launch_bounds__(256) qkv_post_span_kernel(QkvSpanArgs a) {
     const float* src = row + (size_t)hh * dk;
     float x0 = src[c0], x1 = src[c1];
     if (normed) {
-      const float inv = a.whole ? (is_q ? inv_q : inv_k) : 1.0f / sqrtf(head_ss[hh] / (float)dk + a.eps);
+      const float inv = a.whole ? (is_q ? inv_q : inv_k) : 1.0f / sqrtf(head_ss[hh] / (float)a.norm_dim + a.eps);
       const float* gain = is_q ? a.q_gain : a.k_gain;
       const int g0 = a.whole ? (is_q ? hh : hh - H) * dk : 0;
       x0 = (x0 * inv) * gain[g0 + c0];
@@ -433,8 +435,8 @@ __global__ void __launch_bounds__(256) qkv_post_span_quad_kernel(QkvSpanArgs a) 
     }
     sq = block_sum(sq, scratch);
     sk = block_sum(sk, scratch);
-    inv_q = 1.0f / sqrtf(sq / (float)(H * dk) + a.eps);
-    inv_k = 1.0f / sqrtf(sk / (float)(G * dk) + a.eps);
+    inv_q = 1.0f / sqrtf(sq / (float)(H * a.norm_dim) + a.eps);
+    inv_k = 1.0f / sqrtf(sk / (float)(G * a.norm_dim) + a.eps);
   } else if (normed) {
     for (int hh = hh0 + warp; hh < hh1; hh += nwarps) {
       const float* src = row + (size_t)hh * dk;
@@ -454,7 +456,7 @@ __global__ void __launch_bounds__(256) qkv_post_span_quad_kernel(QkvSpanArgs a) 
     if (!is_q && kdst == nullptr) continue;
     float4 x = v[i];
     if (normed) {
-      const float inv = a.whole ? (is_q ? inv_q : inv_k) : 1.0f / sqrtf(head_ss[hh] / (float)dk + a.eps);
+      const float inv = a.whole ? (is_q ? inv_q : inv_k) : 1.0f / sqrtf(head_ss[hh] / (float)a.norm_dim + a.eps);
       x.x = (x.x * inv) * g[i].x; x.y = (x.y * inv) * g[i].y; x.z = (x.z * inv) * g[i].z; x.w = (x.w * inv) * g[i].w;
     }
     if (c < 2 * half_rot) {
@@ -503,7 +505,7 @@ extern "C" int slb_qkv_post_span(const float* qkv, const float* q_gain, const fl
                                  const float* sin_table, void* q_out, void* k_pool, void* v_pool, const int* tok_seq,
                                  const int* tok_pos, const int* block_table, int table_stride, int tokens, int heads,
                                  int kv_heads, int key_dim, int value_dim, int rot_dim, int neighbours, int whole, float eps,
-                                 int dtype, void* stream) {
+                                 int norm_dim, int dtype, void* stream) {
   SLB_REQUIRE(tokens >= 0 && heads > 0 && kv_heads > 0 && heads + kv_heads <= kSpanMaxHeads,
               "qkv_post_span: tokens=%d heads=%d kv_heads=%d (at most %d heads together)", tokens, heads, kv_heads, kSpanMaxHeads);
   SLB_REQUIRE(key_dim > 0 && key_dim % 2 == 0 && value_dim > 0, "qkv_post_span: key size %d must be even, value size %d positive",
@@ -520,6 +522,8 @@ extern "C" int slb_qkv_post_span(const float* qkv, const float* q_gain, const fl
   a.tok_seq = tok_seq; a.tok_pos = tok_pos; a.block_table = block_table; a.table_stride = table_stride;
   a.tokens = tokens; a.heads = heads; a.kv_heads = kv_heads; a.key_dim = key_dim; a.value_dim = value_dim; a.rot_dim = rot_dim;
   a.neighbours = neighbours ? 1 : 0; a.whole = whole ? 1 : 0; a.eps = eps;
+  SLB_REQUIRE(norm_dim >= 0 && norm_dim <= key_dim, "qkv_post_span: %d of %d channels count in the norms", norm_dim, key_dim);
+  a.norm_dim = norm_dim > 0 ? norm_dim : key_dim;
   cudaStream_t s = (cudaStream_t)stream;
   // slices of a token's heads: enough blocks for two per SM when the step brings few tokens (the number depends on the
   // step's size only; which slice handles a head changes nothing in its result)

@@ -153,7 +153,7 @@ _SIGNATURES = {
     "slb_gated_act": [P, P, I, I, I, I, F, F, P],
     "slb_layernorm": [P, P, P, P, P, I, P, I, I, F, P],
     "slb_softcap": [P, L, I, I, F, P],
-    "slb_qkv_post_span": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P],
+    "slb_qkv_post_span": [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, I, P],
     "slb_stream_inject": [P, P, P, I, I, P],
     "slb_latent_post": [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, I, P, P, P],
     "slb_head_prompt_attention": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P],

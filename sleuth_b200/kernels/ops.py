@@ -164,12 +164,14 @@ def qkv_post(qkv, bias, q_gain, k_gain, cos, sin, q_out, k_pool, v_pool, tok_seq
 
 def qkv_post_span(qkv, q_gain, k_gain, cos, sin, q_out, k_pool, v_pool, tok_seq, tok_pos, block_table, heads: int,
                   kv_heads: int, key_dim: int, value_dim: int, rot_dim: int, neighbours: bool, whole: bool, eps: float,
-                  stream=None) -> None:
+                  stream=None, norm_dim: int = 0) -> None:
     """What follows separate q, k and v projections whose float32 results lie side by side in ``qkv``
     [T, heads * key_dim + kv_heads * key_dim + kv_heads * value_dim]: RMS norm of q and k (``whole``: over the whole
     projection with gains of that length; else per head with gains [key_dim]; no gains: none), rotation of each head's
     first ``rot_dim`` channels (``neighbours``: pairs (2i, 2i + 1); else (i, i + rot_dim / 2)), q into ``q_out``
-    [T, heads, key_dim], k and v into the token's cache row (pools [pages, kv_heads, 64, key_dim | value_dim])."""
+    [T, heads, key_dim], k and v into the token's cache row (pools [pages, kv_heads, 64, key_dim | value_dim]).
+    ``norm_dim``: how many channels of a head count in the norms' means, when the heads end in zero channels that only
+    pad them (0 = ``key_dim``)."""
     _cuda(qkv, q_gain, k_gain, cos, sin, q_out, k_pool, v_pool, tok_seq, tok_pos, block_table)
     T = q_out.shape[0]
     _need(qkv.dtype == torch.float32 and qkv.shape == (T, (heads + kv_heads) * key_dim + kv_heads * value_dim),
@@ -191,7 +193,7 @@ def qkv_post_span(qkv, q_gain, k_gain, cos, sin, q_out, k_pool, v_pool, tok_seq,
     _need(tok_seq.dtype == torch.int32 and tok_pos.dtype == torch.int32, "qkv_post_span: token tables are int32")
     lib().call("slb_qkv_post_span", _p(qkv), _p(q_gain), _p(k_gain), _p(cos), _p(sin), _p(q_out), _p(k_pool), _p(v_pool),
                _p(tok_seq), _p(tok_pos), _p(block_table), stride, T, heads, kv_heads, key_dim, value_dim, rot_dim,
-               1 if neighbours else 0, 1 if whole else 0, float(eps), DT[q_out.dtype],
+               1 if neighbours else 0, 1 if whole else 0, float(eps), int(norm_dim), DT[q_out.dtype],
                stream if stream is not None else current_stream())
 
 

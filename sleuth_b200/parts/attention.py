@@ -66,6 +66,13 @@ class GQAAttention(Part):
         self.whole_norm = spec.qk_norm and spec.qk_norm_span == "projection"
         # the wide form: what the per-head kernels (equal widths, per-head norms, halves turned together) do not take
         self.wide = (self.value_dim != spec.head_dim or self.whole_norm or getattr(self.position, "neighbours", False))
+        # The tensor-core attention kernels take keys and values of one width, 64 or 128. A bfloat16 run of the wide form
+        # with other widths up to 128 gives every head zero channels at its end until it has such a width (zero rows in
+        # the projections, zero columns in the output matrix): scores and outputs are the same numbers, the cache rows are
+        # wider, and prompts and single tokens run on the tensor cores instead of the general kernel.
+        self.key_run, self.value_run = spec.head_dim, self.value_dim
+        if self.wide and ctx.dtype == torch.bfloat16 and max(spec.head_dim, self.value_dim) <= 128:
+            self.key_run = self.value_run = 64 if max(spec.head_dim, self.value_dim) <= 64 else 128
         if self.wide and (spec.qkv_bias or spec.reads_shared_kv):
             raise ValueError("attention: biases and a borrowed cache entry are not built for values of another width, "
                              "whole-projection norms or neighbour pairing")
@@ -94,6 +101,9 @@ class GQAAttention(Part):
     def bind(self, t):
         s = self.spec
         names = ["q_proj"] if s.reads_shared_kv else ["q_proj", "k_proj", "v_proj"]
+        if (self.key_run, self.value_run) != (s.head_dim, self.value_dim):
+            self._bind_padded(t)
+            return
         self.qkv = Linear(torch.cat([t[n + ".weight"] for n in names], dim=0), self.ctx.dtype)
         self.o = Linear(t["o_proj.weight"], self.ctx.dtype)
         if s.qkv_bias:
@@ -104,32 +114,59 @@ class GQAAttention(Part):
         if s.sinks:
             self.sinks = t["sinks"].to(torch.float32).contiguous()
 
+    def _bind_padded(self, t):
+        """The wide form's tensors with every head widened by zero channels to ``key_run`` / ``value_run``."""
+        s, dt = self.spec, self.ctx.dtype
+
+        def heads_padded(w, n, width, run):          # [n * width, ...] -> [n * run, ...], zeros behind each head
+            rest = w.shape[1:]
+            out = torch.zeros((n, run, *rest), dtype=w.dtype, device=w.device)
+            out[:, :width] = w.reshape(n, width, *rest)
+            return out.reshape(n * run, *rest)
+
+        q = heads_padded(t["q_proj.weight"], s.heads, s.head_dim, self.key_run)
+        k = heads_padded(t["k_proj.weight"], s.kv_heads, s.head_dim, self.key_run)
+        v = heads_padded(t["v_proj.weight"], s.kv_heads, self.value_dim, self.value_run)
+        self.qkv = Linear(torch.cat([q, k, v], dim=0), dt)
+        o = t["o_proj.weight"]                        # [hidden, heads * value_dim]: zero columns behind each head
+        self.o = Linear(heads_padded(o.t().contiguous(), s.heads, self.value_dim, self.value_run).t().contiguous(), dt)
+        if s.qk_norm:
+            if self.whole_norm:
+                self.q_gain = heads_padded(t["q_norm.weight"], s.heads, s.head_dim, self.key_run).contiguous()
+                self.k_gain = heads_padded(t["k_norm.weight"], s.kv_heads, s.head_dim, self.key_run).contiguous()
+            else:
+                self.q_gain = heads_padded(t["q_norm.weight"], 1, s.head_dim, self.key_run).contiguous()
+                self.k_gain = heads_padded(t["k_norm.weight"], 1, s.head_dim, self.key_run).contiguous()
+        if s.sinks:
+            self.sinks = t["sinks"].to(torch.float32).contiguous()
+
     def cache_request(self):
         s = self.spec
-        return KVRequest(s.kv_heads, s.head_dim, s.window, 0 if self.value_dim == s.head_dim else self.value_dim)
+        return KVRequest(s.kv_heads, self.key_run, s.window, 0 if self.value_run == self.key_run else self.value_run)
 
     # ---- one step ----
     def _attend(self, q, y, b, view, table, ws):
         """Attention of the step's (post-processed) queries over the cache into ``y``; the kernel by dtype and step shape."""
         s = self.spec
-        flash = ops.flash_supported(s.head_dim, self.ctx.dtype) and self.value_dim == s.head_dim
+        hd, vd = self.key_run, self.value_run
+        flash = ops.flash_supported(hd, self.ctx.dtype) and vd == hd
         if not flash:
             ops.attention(q, view.k_pool, view.v_pool, y, b.tok_seq, b.tok_pos, table, s.heads, s.kv_heads,
-                          s.head_dim, view.window, self.scale, b.stream, sinks=self.sinks, value_dim=self.value_dim)
+                          hd, view.window, self.scale, b.stream, sinks=self.sinks, value_dim=vd)
         elif b.max_count == 1:
             splits = ops.decode_splits(b.n, s.kv_heads, s.heads // s.kv_heads, table.shape[1])
-            floats = ops.decode_scratch_floats(b.n, s.heads, s.head_dim, splits)
+            floats = ops.decode_scratch_floats(b.n, s.heads, hd, splits)
             scratch = ws.take((floats,), torch.float32) if floats else None
             ops.attention_decode(q, view.k_pool, view.v_pool, y, b.seq_start, b.past, table, s.heads, s.kv_heads,
-                                 s.head_dim, view.window, self.scale, splits, scratch, b.stream, sinks=self.sinks,
+                                 hd, view.window, self.scale, splits, scratch, b.stream, sinks=self.sinks,
                                  next_read=self.o.weight)
-        elif use_tc_attention(s.heads, s.kv_heads, s.head_dim, self.ctx.dtype, b.max_count, self.scale):
+        elif use_tc_attention(s.heads, s.kv_heads, hd, self.ctx.dtype, b.max_count, self.scale):
             ops.attention_tc(q, view.k_pool, view.v_pool, y, b.seq_start, b.past, b.counts, table, b.max_count,
-                             s.heads, s.kv_heads, s.head_dim, view.window, self.scale, b.stream, max_keys=b.max_len,
+                             s.heads, s.kv_heads, hd, view.window, self.scale, b.stream, max_keys=b.max_len,
                              sinks=self.sinks)
         else:
             ops.attention_prefill(q, view.k_pool, view.v_pool, y, b.seq_start, b.past, b.counts, table, b.max_count,
-                                  s.heads, s.kv_heads, s.head_dim, view.window, self.scale, b.stream, sinks=self.sinks)
+                                  s.heads, s.kv_heads, hd, view.window, self.scale, b.stream, sinks=self.sinks)
 
     def lead_weight(self):
         return self.qkv.weight if self.qkv is not None else None
@@ -212,13 +249,13 @@ class GQAAttention(Part):
         s = self.spec
         T = h.shape[0]
         qkv = self.qkv.forward(h, ws=ws, stream=b.stream, out_dtype=torch.float32)
-        q = ws.take((T, s.heads, s.head_dim), self.ctx.dtype)
+        q = ws.take((T, s.heads, self.key_run), self.ctx.dtype)
         writes = view.writes
         ops.qkv_post_span(qkv, self.q_gain, self.k_gain, cos if rot else None, sin if rot else None, q,
                           view.k_pool if writes else None, view.v_pool if writes else None, b.tok_seq, b.tok_pos, table,
-                          s.heads, s.kv_heads, s.head_dim, self.value_dim, rot, self.position.neighbours, self.whole_norm,
-                          s.qk_norm_eps, b.stream)
-        y = ws.take((T, s.heads * self.value_dim), self.ctx.dtype)
+                          s.heads, s.kv_heads, self.key_run, self.value_run, rot, self.position.neighbours, self.whole_norm,
+                          s.qk_norm_eps, b.stream, norm_dim=s.head_dim)
+        y = ws.take((T, s.heads * self.value_run), self.ctx.dtype)
         self._attend(q, y, b, view, table, ws)
         self.o.forward(y, into=x, ws=ws, stream=b.stream, next_read=getattr(b, "next_read", None))
 

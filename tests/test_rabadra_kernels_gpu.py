@@ -203,6 +203,54 @@ def test_a_far_key_among_hundreds_and_keys_at_page_borders(far, dtype):
         assert float((last - value).abs().max()) < 0.15     # nearly all of the weight lies on the far key
 
 
+@pytest.mark.parametrize("kernel", ["decode", "prefill", "tc"])
+@pytest.mark.parametrize("H, G, hd", [(8, 2, 64), (4, 2, 128), (6, 2, 64)])
+def test_tensor_core_attention_kernels_take_sinks(H, G, hd, kernel):
+    """The split-KV kernel for single tokens (one and several key slices), the mma.sync kernel and the tcgen05 kernels
+    for portions and whole prompts, bfloat16, head sizes 64 and 128: the sink joins each row's denominator once."""
+    o = ops()
+    if kernel == "tc" and not o.attention_tc_supported(H, G, hd, torch.bfloat16):
+        pytest.skip("the tcgen05 kernel does not take this group size")
+    g = torch.Generator().manual_seed(H * hd)
+    dt, scale = torch.bfloat16, hd ** -0.5
+    if kernel == "decode":
+        pasts, counts = [700, 64, 0, 129], [1, 1, 1, 1]
+    else:
+        pasts, counts = [0, 70, 300], [200, 130, 64]
+    seqs = []
+    for p, c in zip(pasts, counts):
+        n = p + c
+        seqs.append({k: torch.randn(n, hh, hd, generator=g).to(dt).double() for k, hh in (("q", H), ("k", G), ("v", G))})
+    sinks = 2.0 * torch.randn(H, generator=g, dtype=torch.float64)
+    k_pool, v_pool, table = kv_pools([s["k"] for s in seqs], [s["v"] for s in seqs], G, hd, hd, dt, 3)
+    T = sum(counts)
+    q = torch.cat([s["q"][p:p + c] for s, p, c in zip(seqs, pasts, counts)]).to(dt).to(DEV).contiguous()
+    out = torch.empty(T, H * hd, dtype=dt, device=DEV)
+    starts = torch.tensor(np.concatenate([[0], np.cumsum(counts)]).astype(np.int32), device=DEV)
+    past_t = torch.tensor(pasts, dtype=torch.int32, device=DEV)
+    count_t = torch.tensor(counts, dtype=torch.int32, device=DEV)
+    sk = sinks.float().to(DEV)
+    want = torch.cat([plain.sink_softmax_attention(s["q"], s["k"], s["v"], scale, sinks)[p:p + c]
+                      for s, p, c in zip(seqs, pasts, counts)]).reshape(T, H * hd)
+    if kernel == "decode":
+        for splits in (1, 3):
+            floats = o.decode_scratch_floats(len(pasts), H, hd, splits)
+            scratch = torch.empty(max(1, floats), dtype=torch.float32, device=DEV)
+            out.zero_()
+            o.attention_decode(q, k_pool, v_pool, out, starts, past_t, table, H, G, hd, 0, scale, splits, scratch, sinks=sk)
+            torch.testing.assert_close(out.cpu().double(), want, **TOL["bf16"])
+    elif kernel == "prefill":
+        o.attention_prefill(q, k_pool, v_pool, out, starts, past_t, count_t, table, max(counts), H, G, hd, 0, scale, sinks=sk)
+        torch.testing.assert_close(out.cpu().double(), want, **TOL["bf16"])
+    else:
+        for wide in (False, True):
+            out.zero_()
+            o.attention_tc(q, k_pool, v_pool, out, starts, past_t, count_t, table, max(counts), H, G, hd, 0, scale, wide=wide,
+                           sinks=sk)
+            o.gemm_tc_check(DEV)
+            torch.testing.assert_close(out.cpu().double(), want, **TOL["bf16"])
+
+
 def route_case(T, d, E, seed):
     g = torch.Generator().manual_seed(seed)
     h = torch.randn(T, d, generator=g)
