@@ -85,3 +85,37 @@ def test_trace_run_refuses_more_tokens_than_it_was_sized_for(model_folders, tmp_
                            "float32", "--out", str(tmp_path / "o"), "--max-tokens", "64"],
                           input=json.dumps(steps[0]) + "\n", capture_output=True, text=True, timeout=120)
     assert proc.returncode != 0 and "64" in proc.stderr
+
+
+def test_trace_run_serves_a_rabadra_folder(rabadra_folders, tmp_path):
+    """The same program with a Rabadra folder, float32: unequal prompts in one batch, then one token each, the shorter
+    request ending first; then another request alone in the room given back."""
+    import tiny_rabadra  # noqa: F401  (the fixture's configurations)
+    from plain import rabadra_plain
+    cfg, w = plain.read_model(rabadra_folders["A"])
+    V = cfg["vocab"]
+    rng = np.random.default_rng(11)
+    reqs = {r: rng.integers(0, V, size=n).tolist() for r, n in (("a", 80), ("b", 9), ("c", 66))}
+    ref = {r: rabadra_plain.forward(cfg, w, ids, torch.float64).float() for r, ids in reqs.items()}
+    cut = {"a": 70, "b": 4}
+    steps = [{"step": 0, "entries": [{"id": r, "tokens": reqs[r][:cut[r]], "want": [cut[r] - 1]} for r in "ab"], "end": []}]
+    expect = {0: [("a", 69), ("b", 3)]}
+    k, live = 1, ["a", "b"]
+    while live:
+        entries, ended = [], []
+        for r in live:
+            pos = cut[r] + k - 1
+            entries.append({"id": r, "tokens": [reqs[r][pos]], "want": [0]})
+            if pos == len(reqs[r]) - 1:
+                ended.append(r)
+        steps.append({"step": k, "entries": entries, "end": ended})
+        expect[k] = [(r, cut[r] + k - 1) for r in live]
+        live = [r for r in live if r not in ended]
+        k += 1
+    steps.append({"step": k, "entries": [{"id": "c", "tokens": reqs["c"], "want": [0, 64, 65]}], "end": ["c"]})
+    expect[k] = [("c", 0), ("c", 64), ("c", 65)]
+    out = tmp_path / "out"
+    replay(rabadra_folders["A"], "float32", steps, out, max_tokens=128 + 64)
+    for step, rows in expect.items():
+        got = np.fromfile(out / f"{step}.f32", dtype="<f4").reshape(len(rows), V)
+        torch.testing.assert_close(torch.from_numpy(got), torch.stack([ref[r][p] for r, p in rows]), rtol=2e-4, atol=2e-4)
