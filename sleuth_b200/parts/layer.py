@@ -10,8 +10,27 @@ itself is a float32 accumulation into the stream, done by the last product of th
 
 from __future__ import annotations
 
+import os
+
+import torch
+
+from ..kernels import ops
 from .base import BuildContext, Normed, Part, build_ffn, build_mixer, build_norm, lead_weight_of, register_layer
 from .spec import LayerSpec
+
+# A parallel layer's mixer and feed-forward read the same x and need nothing from each other. In a step that brings one
+# token a sequence, where a layer is a dozen short kernels that each wait for the one before, the feed-forward runs on
+# a second stream beside the mixer (into a sum of its own that one kernel adds to the stream at the end), so the layer
+# takes as long as its longer branch. Recorded steps keep the fork and the join. SLEUTH_B200_BRANCH=0 turns it off.
+BRANCH = os.environ.get("SLEUTH_B200_BRANCH", "1") != "0"
+_SIDE: dict = {}
+
+
+def _side_stream(device) -> "torch.cuda.Stream":
+    key = torch.device(device).index
+    if key not in _SIDE:
+        _SIDE[key] = torch.cuda.Stream(device=device)
+    return _SIDE[key]
 
 
 class PreNormLayer(Part):
@@ -104,12 +123,38 @@ class ParallelLayer(Part):
         if h is None:
             h = Normed(self.norm1, x, ws, b.stream, self.ctx.dtype).tensor()
             h2 = Normed(self.norm2, x, ws, b.stream, self.ctx.dtype).tensor() if self.norm2 is not None else h
+        if self.ffn is not None and BRANCH and b.max_count == 1:
+            self._forward_branches(h, h2, x, b, view, ws, after)
+            ws.release(mark)
+            return
         b.next_read = lead_weight_of(self.ffn) if self.ffn is not None else after
         self.mixer.forward(h, x, b, view, ws)
         b.next_read = after
         if self.ffn is not None:
             self.ffn.forward(h2, x, b, ws)
         ws.release(mark)
+
+    def _forward_branches(self, h, h2, x, b, view, ws, after):
+        """The feed-forward on a second stream into a sum of its own, the mixer on this one into the stream, then
+        x += that sum. The two branches' scratch memory must not overlap: the feed-forward's is taken first, and the
+        mixer's begins above the highest address the feed-forward used."""
+        main = torch.cuda.current_stream()
+        side = _side_stream(x.device)
+        x2 = ws.take(x.shape, torch.float32)
+        seen, ws.high = ws.high, ws.top
+        side.wait_stream(main)                  # the norms' outputs are ready
+        b.next_read = None
+        with torch.cuda.stream(side):
+            b.stream = side.cuda_stream
+            x2.zero_()
+            self.ffn.forward(h2, x2, b, ws)
+        b.stream = main.cuda_stream
+        ws.top = max(ws.top, ws.high)
+        ws.high = max(seen, ws.high)
+        b.next_read = after
+        self.mixer.forward(h, x, b, view, ws)
+        main.wait_stream(side)
+        ops.add(x, x2, stream=b.stream)
 
 
 register_layer("prenorm", PreNormLayer)
