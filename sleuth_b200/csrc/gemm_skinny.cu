@@ -242,7 +242,7 @@ __global__ void __launch_bounds__(kSkinnyWarps * 32, (MODE != kSwiglu && NF == 1
       float u = 0.0f;
 #pragma unroll
       for (int w8 = 0; w8 < kSkinnyWarps; ++w8) u += red[w8][NF + f][r][cc];
-      v = gated(a.gate, v, u);
+      v = a.gate.kind == kGateSilu ? (v / (1.0f + expf(-v))) * u : gated(a.gate, v, u);
       reinterpret_cast<__nv_bfloat16*>(a.C)[(size_t)r * a.ldc + feat] = __float2bfloat16_rn(v);
     } else if (MODE == kStoreBf16) {
       reinterpret_cast<__nv_bfloat16*>(a.C)[(size_t)r * a.ldc + feat] = __float2bfloat16_rn(v);

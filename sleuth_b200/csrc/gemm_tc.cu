@@ -518,10 +518,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         if (gated) {
           uint32_t u[32];
           tmem_ld32(lane_base + BN / 2 + c, u);
+          if (a.gate.kind == kGateSilu) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            v[j] = a.gate.kind == kGateSilu ? fast_silu(__uint_as_float(r[j])) * __uint_as_float(u[j])
-                                            : fast_gated(a.gate, __uint_as_float(r[j]), __uint_as_float(u[j]));
+            for (int j = 0; j < 32; ++j) v[j] = fast_silu(__uint_as_float(r[j])) * __uint_as_float(u[j]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = fast_gated(a.gate, __uint_as_float(r[j]), __uint_as_float(u[j]));
+          }
         } else {
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
